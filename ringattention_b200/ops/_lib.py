@@ -1,0 +1,116 @@
+"""ctypes binding of the sm_100a kernel library (``_C/libringattn_b200.so``).
+
+The library is built in-tree by :mod:`ringattention_b200._build`. On a machine with a CUDA device
+the ops of this package *require* it: :func:`lib` raises if it cannot be loaded, there is no silent
+PyTorch fallback on the GPU path. Every launcher returns 0 on success or a negative host error
+code; device-side problems (a bounded wait that ran out) are reported through a per-device int32
+status word that :func:`check_status` reads.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+_STATUS: dict[int, torch.Tensor] = {}
+_LAUNCHES = 0
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "_C" / "libringattn_b200.so"
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "timeout waiting for a TMA-filled shared-memory stage",
+    2: "timeout waiting for a shared-memory stage to be released",
+    3: "timeout waiting for a TMEM accumulator to be produced",
+    4: "timeout waiting for a TMEM accumulator to be drained",
+    5: "timeout waiting for a peer flag",
+    6: "timeout (other)",
+    7: "bad argument seen on the device",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    """True when the shared object exists (it may still be unusable without a GPU)."""
+    return LIB_PATH.exists()
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the kernel library; build it first if it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not LIB_PATH.exists():
+            if os.environ.get("RINGATTN_B200_NO_AUTOBUILD") == "1":
+                raise KernelError(f"{LIB_PATH} is missing; run python -m ringattention_b200._build")
+            from .. import _build
+
+            _build.build()
+        handle = ctypes.CDLL(str(LIB_PATH))
+        handle.ra_last_error.restype = ctypes.c_char_p
+        _LIB = handle
+    return _LIB
+
+
+def status_tensor(device: torch.device | int | None = None) -> torch.Tensor:
+    """The int32 status word kernels write to on ``device`` (allocated once per device)."""
+    if device is None:
+        idx = torch.cuda.current_device()
+    elif isinstance(device, int):
+        idx = device
+    else:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _STATUS.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
+        _STATUS[idx] = t
+    return t
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Synchronise and raise :class:`KernelError` if any kernel recorded a failure."""
+    t = status_tensor(device)
+    code = int(t[0].item())
+    if code != 0:
+        if reset:
+            t.zero_()
+        raise KernelError(f"device status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def launches() -> int:
+    """Number of kernels of this library launched so far in this process."""
+    return _LAUNCHES
+
+
+def count_launch(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def call(name: str, *args, n_kernels: int = 1) -> None:
+    """Call launcher ``name``; raise with the library's message on a non-zero return code."""
+    fn = getattr(lib(), name)
+    rc = fn(*args)
+    if rc != 0:
+        msg = lib().ra_last_error()
+        raise KernelError(f"{name} failed ({rc}): {msg.decode() if msg else ''}")
+    count_launch(n_kernels)
