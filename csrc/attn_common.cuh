@@ -1,0 +1,97 @@
+// Shared pieces of the attention kernels: position maps, tile visibility, dropout hash.
+#pragma once
+#include "common/sm100.cuh"
+
+namespace ra {
+namespace attn {
+
+// Global token position of local index i. A shard is one contiguous run (half >= length) or two
+// runs of `half` tokens each (zig-zag layout); `half` is a multiple of the 128-row tile.
+struct PosMap {
+  int off0;
+  int off1;
+  int half;
+  __device__ __forceinline__ int operator()(int i) const {
+    return i < half ? off0 + i : off1 + (i - half);
+  }
+};
+
+struct MaskParams {
+  int Sq, Sk;
+  int cbs;  // causal block size, 0 = not causal
+  PosMap qmap, kmap;
+  const int* seg_q;     // (B, Sq) segment ids of the local queries, or null
+  const int* seg_k;     // (B, Sk) segment ids of this KV block, or null
+  const int* seg_q_mm;  // (B, ceil(Sq/128), 2) per-tile {min, max} segment id, or null
+  const int* seg_k_mm;  // (B, ceil(Sk/128), 2)
+  const float* bias;    // (B, Hb, Sk) additive key bias in natural-log units, or null
+  long long bias_stride_b, bias_stride_h;
+  unsigned int seed_lo, seed_hi;
+  unsigned int drop_threshold;  // 0 = dropout off; logit dropped iff hash < threshold
+};
+
+// False when every entry of the (128 q x 128 k) tile is masked by the causal rule or because the
+// segment-id ranges of the two tiles are disjoint. qi0/k0 are local start indices.
+__device__ __forceinline__ bool tile_visible(const MaskParams& m, int b, int qi0, int k0) {
+  if (qi0 >= m.Sq || k0 >= m.Sk) return false;
+  if (m.cbs) {
+    const int q_hi = m.qmap(min(qi0 + 127, m.Sq - 1));
+    const int k_lo = m.kmap(k0);
+    if (q_hi / m.cbs < k_lo / m.cbs) return false;
+  }
+  if (m.seg_q_mm) {
+    const int nqt = (m.Sq + 127) >> 7, nkt = (m.Sk + 127) >> 7;
+    const int* qm = m.seg_q_mm + (static_cast<long long>(b) * nqt + (qi0 >> 7)) * 2;
+    const int* km = m.seg_k_mm + (static_cast<long long>(b) * nkt + (k0 >> 7)) * 2;
+    if (qm[1] < km[0] || km[1] < qm[0]) return false;
+  }
+  return true;
+}
+
+// True when no entry of the tile needs element-wise masking or bias.
+__device__ __forceinline__ bool tile_plain(const MaskParams& m, int qi0, int k0) {
+  if (m.seg_q || m.bias || m.drop_threshold) return false;
+  if (k0 + 128 > m.Sk) return false;
+  if (m.cbs) {
+    const int q_lo = m.qmap(qi0);
+    const int k_hi = m.kmap(min(k0 + 127, m.Sk - 1));
+    if (q_lo / m.cbs < k_hi / m.cbs) return false;
+  }
+  return true;
+}
+
+// Number of leading columns of the k tile that the causal rule and the sequence end leave
+// visible to a query at global position qpos: column c is masked iff c >= limit.
+__device__ __forceinline__ int causal_col_limit(const MaskParams& m, int qpos, int k0) {
+  int limit = m.Sk - k0;
+  if (m.cbs) {
+    const int kbase = m.kmap(k0);
+    const long long lim = (static_cast<long long>(qpos / m.cbs) + 1) * m.cbs - kbase;
+    limit = static_cast<int>(lim < limit ? (lim < 0 ? 0 : lim) : limit);
+  }
+  return limit;
+}
+
+__device__ __forceinline__ unsigned int mix32(unsigned int x) {
+  x ^= x >> 16;
+  x *= 0x7FEB352Du;
+  x ^= x >> 15;
+  x *= 0x846CA68Bu;
+  x ^= x >> 16;
+  return x;
+}
+// Counter-based dropout hash of (seed, b*H+h, q position, k position).
+__device__ __forceinline__ unsigned int dropout_hash(unsigned int seed_lo, unsigned int seed_hi,
+                                                     unsigned int bh, unsigned int qpos,
+                                                     unsigned int kpos) {
+  unsigned int x = qpos * 0x9E3779B1u + kpos * 0x85EBCA77u + bh * 0xC2B2AE3Du + seed_lo;
+  x = mix32(x);
+  x = mix32((x ^ seed_hi) + kpos);
+  return x;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace attn
+}  // namespace ra
