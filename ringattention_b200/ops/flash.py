@@ -155,3 +155,83 @@ def flash_fwd(q, k, v, mask: MaskSpec, *, o_prev=None, lse_prev=None, out_fp32=F
     a.stream = torch.cuda.current_stream().cuda_stream
     _lib.call("ra_attn_fwd", ctypes.byref(a))
     return out, lse_out
+
+
+class _BwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_vp), ("k", c_vp), ("v", c_vp), ("d_o", c_vp),
+        ("q_sb", c_ll), ("q_ss", c_ll), ("q_sh", c_ll),
+        ("k_sb", c_ll), ("k_ss", c_ll), ("k_sh", c_ll),
+        ("v_sb", c_ll), ("v_ss", c_ll), ("v_sh", c_ll),
+        ("do_sb", c_ll), ("do_ss", c_ll), ("do_sh", c_ll),
+        ("lse2", c_vp), ("delta", c_vp), ("Sq_pad", ctypes.c_int),
+        ("dq_acc", c_vp),
+        ("dk", c_vp), ("dv", c_vp), ("dkv_sb", c_ll), ("dkv_ss", c_ll), ("dkv_sh", c_ll),
+        ("dkv_mode", ctypes.c_int),
+        ("B", ctypes.c_int), ("H", ctypes.c_int), ("Sq", ctypes.c_int), ("Sk", ctypes.c_int),
+        ("D", ctypes.c_int),
+        ("softmax_scale", ctypes.c_float),
+        ("causal_block_size", ctypes.c_int),
+        ("q_off0", ctypes.c_int), ("q_off1", ctypes.c_int), ("q_half", ctypes.c_int),
+        ("k_off0", ctypes.c_int), ("k_off1", ctypes.c_int), ("k_half", ctypes.c_int),
+        ("seg_q", c_vp), ("seg_k", c_vp), ("seg_q_mm", c_vp), ("seg_k_mm", c_vp),
+        ("bias", c_vp), ("bias_sb", c_ll), ("bias_sh", c_ll),
+        ("seed", ctypes.c_ulonglong), ("drop_threshold", ctypes.c_uint),
+        ("copy_src", c_vp), ("copy_dst", c_vp), ("copy_bytes", c_ll), ("copy_ctas", ctypes.c_int),
+        ("status", c_vp),
+        ("stream", c_vp),
+    ]
+
+
+DKV_STORE_BF16 = 0
+DKV_STORE_FP32 = 1
+DKV_REDUCE_FP32 = 2
+
+
+def flash_bwd_prep(out, dout, lse):
+    """``delta = rowsum(dO*O)`` and ``lse*log2(e)`` in ``(B, H, Sq_pad)`` fp32 buffers (padded to a
+    multiple of 128 queries; padding and fully masked rows get ``+inf`` / 0)."""
+    _check_bshd(out, "out"); _check_bshd(dout, "dout")
+    B, Sq, H, D = out.shape
+    sq_pad = (Sq + 127) // 128 * 128
+    lse2 = torch.empty(B, H, sq_pad, device=out.device, dtype=torch.float32)
+    delta = torch.empty(B, H, sq_pad, device=out.device, dtype=torch.float32)
+    assert lse.dtype == torch.float32 and lse.is_contiguous() and lse.shape == (B, H, Sq)
+    _lib.call("ra_attn_bwd_prep", c_vp(out.data_ptr()), c_ll(out.stride(0)), c_ll(out.stride(1)),
+              c_ll(out.stride(2)), c_vp(dout.data_ptr()), c_ll(dout.stride(0)), c_ll(dout.stride(1)),
+              c_ll(dout.stride(2)), c_vp(lse.data_ptr()), c_vp(lse2.data_ptr()),
+              c_vp(delta.data_ptr()), B, H, Sq, sq_pad, D, _lib.stream_ptr())
+    return lse2, delta
+
+
+def flash_bwd(q, k, v, dout, lse2, delta, mask: MaskSpec, dq_acc, dk, dv, dkv_mode=DKV_STORE_BF16,
+              *, copy_src: int = 0, copy_dst: int = 0, copy_bytes: int = 0, copy_ctas: int = 8):
+    """One ring step of the backward. ``dq_acc`` (fp32, contiguous, pre-zeroed by the caller before
+    the first step) receives ``dQ`` by reduction; ``dk``/``dv`` are written according to
+    ``dkv_mode`` (store bf16, store fp32, or fp32 reduction into possibly remote memory)."""
+    _check_bshd(q, "q"); _check_bshd(k, "k"); _check_bshd(v, "v"); _check_bshd(dout, "dout")
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    dev = q.device
+    assert dq_acc.dtype == torch.float32 and dq_acc.is_contiguous() and dq_acc.shape == q.shape
+    assert dk.shape == k.shape and dv.shape == k.shape and dk.stride() == dv.stride()
+    want = torch.bfloat16 if dkv_mode == DKV_STORE_BF16 else torch.float32
+    assert dk.dtype == want and dv.dtype == want and dk.stride(3) == 1
+    a = _BwdArgs()
+    a.q, a.k, a.v, a.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
+    a.q_sb, a.q_ss, a.q_sh = q.stride(0), q.stride(1), q.stride(2)
+    a.k_sb, a.k_ss, a.k_sh = k.stride(0), k.stride(1), k.stride(2)
+    a.v_sb, a.v_ss, a.v_sh = v.stride(0), v.stride(1), v.stride(2)
+    a.do_sb, a.do_ss, a.do_sh = dout.stride(0), dout.stride(1), dout.stride(2)
+    a.lse2, a.delta, a.Sq_pad = lse2.data_ptr(), delta.data_ptr(), lse2.shape[2]
+    a.dq_acc = dq_acc.data_ptr()
+    a.dk, a.dv = dk.data_ptr(), dv.data_ptr()
+    a.dkv_sb, a.dkv_ss, a.dkv_sh = dk.stride(0), dk.stride(1), dk.stride(2)
+    a.dkv_mode = dkv_mode
+    a.B, a.H, a.Sq, a.Sk, a.D = B, H, Sq, Sk, D
+    a.softmax_scale = 1.0 / math.sqrt(D)
+    _fill_mask(a, mask, H)
+    a.copy_src, a.copy_dst, a.copy_bytes, a.copy_ctas = copy_src, copy_dst, copy_bytes, copy_ctas
+    a.status = _lib.status_tensor(dev).data_ptr()
+    a.stream = torch.cuda.current_stream().cuda_stream
+    _lib.call("ra_attn_bwd", ctypes.byref(a))
