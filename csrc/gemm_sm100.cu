@@ -31,7 +31,8 @@ struct Params {
   long long ldc;
   int M, N, K;
   int c_fp32;   // 1: C is fp32, 0: bf16
-  int beta;     // 1: C += A B^T, 0: C = A B^T
+  const void* R;  // optional addend with C's element type: C = A B^T + R (R may alias C)
+  long long ldr;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of B across the group)
   int* status;
 };
@@ -210,8 +211,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + j * 4 < p.N) {
                 float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (p.beta) {
-                  const float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
+                if (p.R) {
+                  const float4 o = *reinterpret_cast<const float4*>(
+                      reinterpret_cast<const float*>(p.R) + static_cast<long long>(row) * p.ldr + col0 + 4 * j);
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
                 *reinterpret_cast<float4*>(dst + 4 * j) = v;
@@ -226,8 +228,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
-                if (p.beta) {
-                  const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
+                if (p.R) {
+                  const uint4 o = *reinterpret_cast<const uint4*>(
+                      reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<long long>(row) * p.ldr + col0 + 8 * j);
                   const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
@@ -283,16 +286,19 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaSt
 }  // namespace gemm
 }  // namespace ra
 
-// C[M,N] (ldc) = A * B^T (+ C). a_mn = 0: A is [M][lda] (K contiguous); 1: A is [K][lda] (M
+// C[M,N] (ldc) = A * B^T (+ R). a_mn = 0: A is [M][lda] (K contiguous); 1: A is [K][lda] (M
 // contiguous). b_mn = 0: B is [N][ldb]; 1: B is [K][ldb]. All leading dimensions in elements and
-// multiples of 8; base pointers 16-byte aligned. c_fp32 selects the output type.
-extern "C" int ra_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
-                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
-                            int c_fp32, int beta, int group_m, int* status, void* stream) {
+// multiples of 8; base pointers 16-byte aligned. c_fp32 selects the type of C and R. R is an
+// optional addend (residual or running gradient) and may alias C for in-place accumulation.
+extern "C" int ra_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N,
+                            int K, long long lda, long long ldb, long long ldc, long long ldr,
+                            int a_mn, int b_mn, int c_fp32, int group_m, int* status,
+                            void* stream) {
   using namespace ra;
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (ldc % (c_fp32 ? 4 : 8)) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
-      (reinterpret_cast<uintptr_t>(C) & 15)) {
+      (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(R) & 15) ||
+      (R && (ldr % (c_fp32 ? 4 : 8)))) {
     set_error("ra_gemm_bf16: bad shape/alignment");
     return kHostBadArg;
   }
@@ -310,7 +316,7 @@ extern "C" int ra_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     str[0] = static_cast<uint64_t>(ldb) * 2;
     if ((rc = make_tmap_bf16_sw128(&tb, B, 2, dims, str, box)) != 0) return rc;
   }
-  gemm::Params p{C, ldc, M, N, K, c_fp32, beta, group_m > 0 ? group_m : 8, status};
+  gemm::Params p{C, ldc, M, N, K, c_fp32, R, ldr, group_m > 0 ? group_m : 8, status};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!a_mn && !b_mn) return gemm::launch<0, 0>(ta, tb, p, s);
   if (!a_mn && b_mn) return gemm::launch<0, 1>(ta, tb, p, s);

@@ -1,0 +1,288 @@
+"""LLaMA-style decoder driven by the sm_100a kernels, with hand-written forward and backward.
+
+The reference has no model; its README shows the op inside an external LLaMA (LWM) on a
+``(dp, fsdp, tp, sp)`` mesh (README.md:19-49,62). This driver supplies that model: RMSNorm, fused
+QKV projection, RoPE, ring attention, output projection with the residual add in the GEMM epilogue,
+blockwise SwiGLU feed-forward (chunk loop, ringattention_jax.py:333-352), chunked LM head fused with
+the loss. Parameters live in flat buffers (fp32 master + moments + grads, bf16 working copy) so the
+optimizer, the gradient all-reduce and checkpoints are single operations.
+
+Remat policy ``nothing_saveable`` (ringattention_jax.py:334) keeps only the layer inputs and
+recomputes each layer, attention included, in the backward pass. ``everything_saveable`` keeps the
+per-layer activations that backward needs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import POLICY_NOTHING_SAVEABLE, BlockwiseKwargs, LlamaConfig
+from ..ops import attention as A
+from ..ops import kernels as K
+from ..ops.flash import Positions
+from ..ops.reference import shard_segments
+
+
+class FlatParams:
+    """Flat parameter storage. Matrices come first (weight decay applies to ``[0, decay_end)``),
+    norm gains last. ``shard`` = (index, count) keeps only a contiguous 1/count slice of the
+    optimizer state (fp32 master, moments); the bf16 working copy and the grads stay full-size."""
+
+    def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
+                 shard: Tuple[int, int] = (0, 1)):
+        self.cfg = cfg
+        self.device = device
+        d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+        self.index: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
+        off = 0
+
+        def add(name, shape):
+            nonlocal off
+            n = math.prod(shape)
+            self.index[name] = (off, shape)
+            off += (n + 63) // 64 * 64  # keep every tensor 256-byte aligned in bf16 and fp32
+
+        add("embed", (V, d))
+        for l in range(cfg.n_layers):
+            add(f"l{l}.wqkv", (3 * d, d))
+            add(f"l{l}.wo", (d, d))
+            add(f"l{l}.wgu", (2 * F, d))
+            add(f"l{l}.wd", (d, F))
+        add("lm_head", (V, d))
+        self.decay_end = off
+        for l in range(cfg.n_layers):
+            add(f"l{l}.n1", (d,))
+            add(f"l{l}.n2", (d,))
+        add("nf", (d,))
+        self.numel = (off + 1023) // 1024 * 1024
+        self.shard_index, self.shard_count = shard
+        if self.numel % (self.shard_count * 4):
+            self.numel = (self.numel + self.shard_count * 1024 - 1) // (self.shard_count * 1024) * (self.shard_count * 1024)
+        self.p16 = torch.empty(self.numel, device=device, dtype=torch.bfloat16)
+        self.g32: Optional[torch.Tensor] = None
+        self._init_weights(seed)
+        self.p32 = self.m = self.v = None
+        if with_optimizer:
+            lo, hi = self.shard_range()
+            self.p32 = self.p16[lo:hi].float()
+            self.m = torch.zeros(hi - lo, device=device, dtype=torch.float32)
+            self.v = torch.zeros(hi - lo, device=device, dtype=torch.float32)
+
+    def shard_range(self) -> Tuple[int, int]:
+        n = self.numel // self.shard_count
+        return self.shard_index * n, (self.shard_index + 1) * n
+
+    def _init_weights(self, seed: int) -> None:
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        self.p16.zero_()
+        chunk = 1 << 26
+        # N(0, init_std) for matrices, drawn in fp32 chunks to bound peak memory
+        for s0 in range(0, self.decay_end, chunk):
+            n = min(chunk, self.decay_end - s0)
+            self.p16[s0:s0 + n] = (torch.randn(n, device=self.device, generator=gen) * self.cfg.init_std).bfloat16()
+        self.p16[self.decay_end:] = 0
+        for name, (off, shape) in self.index.items():
+            if len(shape) == 1:
+                self.p16[off:off + shape[0]] = 1.0
+
+    def ensure_grads(self) -> torch.Tensor:
+        if self.g32 is None:
+            self.g32 = torch.zeros(self.numel, device=self.device, dtype=torch.float32)
+        return self.g32
+
+    def w(self, name: str) -> torch.Tensor:
+        off, shape = self.index[name]
+        return self.p16[off:off + math.prod(shape)].view(shape)
+
+    def g(self, name: str) -> torch.Tensor:
+        off, shape = self.index[name]
+        return self.g32[off:off + math.prod(shape)].view(shape)
+
+    def n_params(self) -> int:
+        return sum(math.prod(s) for _, s in self.index.values())
+
+
+@dataclass
+class StepContext:
+    """Per-step sharding information shared by all layers."""
+
+    B: int
+    S: int                      # local sequence length
+    plan: A.RingPlan
+    positions: Positions        # global positions of the local tokens (RoPE, masks)
+    symm_ring: object = None
+    total_tokens: int = 0       # number of target tokens in the whole global batch
+
+
+class LlamaModel:
+    """Forward/backward of the decoder on one rank's token shard."""
+
+    def __init__(self, cfg: LlamaConfig, device="cuda", seed: int = 0, with_optimizer: bool = True,
+                 params: Optional[FlatParams] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.params = params if params is not None else FlatParams(cfg, self.device, seed, with_optimizer)
+        self.H, self.D = cfg.n_heads, cfg.head_dim
+        if self.D not in (64, 128):
+            raise ValueError("head_dim must be 64 or 128 for the fused attention kernels")
+
+    # ------------------------------------------------------------------ context
+    def make_context(self, B: int, S_local: int, rank: int = 0, world: int = 1, segment_ids=None,
+                     symm_ring=None, total_tokens: Optional[int] = None) -> StepContext:
+        kw = BlockwiseKwargs(causal_block_size=self.cfg.causal_block_size,
+                             query_chunk_size=min(self.cfg.query_chunk_size, S_local),
+                             key_chunk_size=min(self.cfg.key_chunk_size, S_local),
+                             layout=self.cfg.layout)
+        plan = A.make_plan(rank, world, B, S_local, S_local, self.H, kw, segment_ids=segment_ids,
+                           device=self.device)
+        pos = Positions.from_segments(shard_segments(rank, world, S_local, self.cfg.layout))
+        return StepContext(B=B, S=S_local, plan=plan, positions=pos, symm_ring=symm_ring,
+                           total_tokens=total_tokens if total_tokens is not None else B * S_local * world)
+
+    # ------------------------------------------------------------------ layer forward
+    def _attn_block_fwd(self, l: int, x: torch.Tensor, ctx: StepContext):
+        cfg, P = self.cfg, self.params
+        B, S, H, D, d = ctx.B, ctx.S, self.H, self.D, cfg.d_model
+        h1, rstd1 = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
+        qkv = K.linear_fwd(h1, P.w(f"l{l}.wqkv"))
+        qkv5 = qkv.view(B, S, 3, H, D)
+        qk = qkv.view(B, S, 3 * H, D)[:, :, :2 * H]  # q heads then k heads
+        K.rope_(qk, ctx.positions, cfg.rope_theta)
+        q, k, v = qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]
+        attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
+        x2 = K.linear_fwd(attn.view(B * S, d), P.w(f"l{l}.wo"), residual=x)
+        return x2, (h1, rstd1, qkv, attn, lse)
+
+    def _ffn_fwd(self, l: int, x2: torch.Tensor, h2: torch.Tensor) -> torch.Tensor:
+        cfg, P = self.cfg, self.params
+        M = x2.shape[0]
+        x3 = torch.empty_like(x2)
+        step = min(cfg.ffn_chunk_size, M)
+        wgu, wd = P.w(f"l{l}.wgu"), P.w(f"l{l}.wd")
+        for r0 in range(0, M, step):
+            r1 = min(M, r0 + step)
+            gu = K.linear_fwd(h2[r0:r1], wgu)
+            a = K.swiglu_fwd(gu)
+            K.linear_fwd(a, wd, out=x3[r0:r1], residual=x2[r0:r1])
+        return x3
+
+    def layer_forward(self, l: int, x: torch.Tensor, ctx: StepContext, keep: bool = False):
+        x2, saved = self._attn_block_fwd(l, x, ctx)
+        h2, rstd2 = K.rmsnorm_fwd(x2, self.params.w(f"l{l}.n2"), self.cfg.rms_eps)
+        x3 = self._ffn_fwd(l, x2, h2)
+        if keep:
+            return x3, saved + (x2, h2, rstd2)
+        return x3, None
+
+    # ------------------------------------------------------------------ layer backward
+    def layer_backward(self, l: int, x: torch.Tensor, dx3: torch.Tensor, ctx: StepContext, saved=None):
+        cfg, P = self.cfg, self.params
+        B, S, H, D, d = ctx.B, ctx.S, self.H, self.D, cfg.d_model
+        M = B * S
+        if saved is None:  # nothing_saveable: recompute the layer up to the FFN input
+            x2, s = self._attn_block_fwd(l, x, ctx)
+            h2, rstd2 = K.rmsnorm_fwd(x2, P.w(f"l{l}.n2"), cfg.rms_eps)
+            saved = s + (x2, h2, rstd2)
+        h1, rstd1, qkv, attn, lse, x2, h2, rstd2 = saved
+        wgu, wd = P.w(f"l{l}.wgu"), P.w(f"l{l}.wd")
+        # ---- blockwise FFN backward (each chunk recomputes its activations)
+        dh2 = torch.empty_like(x2)
+        step = min(cfg.ffn_chunk_size, M)
+        for r0 in range(0, M, step):
+            r1 = min(M, r0 + step)
+            gu = K.linear_fwd(h2[r0:r1], wgu)
+            a = K.swiglu_fwd(gu)
+            da = K.linear_dgrad(dx3[r0:r1], wd)
+            K.linear_wgrad(dx3[r0:r1], a, P.g(f"l{l}.wd"))
+            K.swiglu_bwd_(gu, da)
+            K.linear_wgrad(gu, h2[r0:r1], P.g(f"l{l}.wgu"))
+            K.linear_dgrad(gu, wgu, out=dh2[r0:r1])
+        dx2 = K.rmsnorm_bwd(dh2, x2, P.w(f"l{l}.n2"), rstd2, P.g(f"l{l}.n2"), dres=dx3)
+        del dh2
+        # ---- attention block backward
+        attn2 = attn.view(M, d)
+        dattn = K.linear_dgrad(dx2, P.w(f"l{l}.wo"))
+        K.linear_wgrad(dx2, attn2, P.g(f"l{l}.wo"))
+        qkv5 = qkv.view(B, S, 3, H, D)
+        dqkv = torch.empty_like(qkv)
+        dqkv5 = dqkv.view(B, S, 3, H, D)
+        A.ring_backward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], attn, lse, dattn.view(B, S, H, D),
+                        ctx.plan, ctx.symm_ring, dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
+        K.rope_(dqkv.view(B, S, 3 * H, D)[:, :, :2 * H], ctx.positions, cfg.rope_theta, inverse=True)
+        K.linear_wgrad(dqkv, h1, P.g(f"l{l}.wqkv"))
+        dh1 = K.linear_dgrad(dqkv, P.w(f"l{l}.wqkv"))
+        dx = K.rmsnorm_bwd(dh1, x, P.w(f"l{l}.n1"), rstd1, P.g(f"l{l}.n1"), dres=dx2)
+        return dx
+
+    # ------------------------------------------------------------------ head (final norm + LM head + loss)
+    def head_forward_backward(self, x: torch.Tensor, targets: torch.Tensor, ctx: StepContext,
+                              compute_grad: bool = True):
+        """Returns ``(sum of token losses on this rank, dx)``. The LM head runs in token chunks;
+        each chunk's logits are turned into dlogits in place and consumed immediately."""
+        cfg, P = self.cfg, self.params
+        M = x.shape[0]
+        hf, rstdf = K.rmsnorm_fwd(x, P.w("nf"), cfg.rms_eps)
+        dhf = torch.empty_like(x) if compute_grad else None
+        wlm = P.w("lm_head")
+        losses = torch.empty(M, device=x.device, dtype=torch.float32)
+        step = min(cfg.loss_chunk_size, M)
+        scale = 1.0 / max(1, ctx.total_tokens)
+        tflat = targets.reshape(-1)
+        for r0 in range(0, M, step):
+            r1 = min(M, r0 + step)
+            logits = K.linear_fwd(hf[r0:r1], wlm)
+            K.xent_fwd_bwd_(logits, tflat[r0:r1], scale, loss=losses[r0:r1])
+            if compute_grad:
+                K.linear_wgrad(logits, hf[r0:r1], P.g("lm_head"))
+                K.linear_dgrad(logits, wlm, out=dhf[r0:r1])
+        loss_sum = losses.sum()
+        if not compute_grad:
+            return loss_sum, None
+        dx = K.rmsnorm_bwd(dhf, x, P.w("nf"), rstdf, P.g("nf"))
+        return loss_sum, dx
+
+    # ------------------------------------------------------------------ full passes
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor, ctx: StepContext):
+        """One training forward+backward on this rank's shard. ``tokens``/``targets`` are
+        ``(B, S_local)`` int32 (targets < 0 are ignored). Gradients are *added* to the flat fp32
+        grad buffer; returns the local sum of token losses (a 0-d tensor)."""
+        cfg, P = self.cfg, self.params
+        P.ensure_grads()
+        tok = tokens.reshape(-1).contiguous()
+        x = K.embedding_fwd(tok, P.w("embed"))
+        keep = cfg.remat != POLICY_NOTHING_SAVEABLE
+        layer_inputs: List[torch.Tensor] = []
+        saved_all: List[object] = []
+        for l in range(cfg.n_layers):
+            layer_inputs.append(x)
+            x, saved = self.layer_forward(l, x, ctx, keep=keep)
+            saved_all.append(saved)
+        loss_sum, dx = self.head_forward_backward(x, targets, ctx)
+        del x
+        for l in reversed(range(cfg.n_layers)):
+            dx = self.layer_backward(l, layer_inputs[l], dx, ctx, saved_all[l])
+            layer_inputs[l] = None
+            saved_all[l] = None
+        K.embedding_bwd(tok, dx, P.g("embed"))
+        return loss_sum
+
+    @torch.no_grad()
+    def forward_loss(self, tokens, targets, ctx: StepContext):
+        """Forward only; returns the local sum of token losses."""
+        x = K.embedding_fwd(tokens.reshape(-1).contiguous(), self.params.w("embed"))
+        for l in range(self.cfg.n_layers):
+            x, _ = self.layer_forward(l, x, ctx)
+        loss_sum, _ = self.head_forward_backward(x, targets, ctx, compute_grad=False)
+        return loss_sum
+
+    def flops_per_token(self, seq_len_global: int, causal: bool = True) -> float:
+        """Model FLOPs per token for forward+backward (6 * matmul params + attention)."""
+        cfg = self.cfg
+        d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+        mm = cfg.n_layers * (4 * d * d + 3 * d * F) + V * d
+        attn = cfg.n_layers * 2 * seq_len_global * d * (0.5 if causal else 1.0) * 2  # QK^T and PV
+        return 6.0 * mm + 3.0 * attn

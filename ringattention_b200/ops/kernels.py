@@ -1,0 +1,193 @@
+"""Typed Python wrappers over the C launchers (GEMM and the memory-bound driver kernels).
+
+All functions take CUDA tensors, launch on the current stream and return their outputs; they never
+fall back to PyTorch math. Shapes follow the LLaMA driver: activations are ``(rows, d)`` bf16.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import ptr, stream_ptr
+
+c_ll = ctypes.c_longlong
+c_f = ctypes.c_float
+
+
+def _status():
+    return ptr(_lib.status_tensor())
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, group_m: int = 8) -> torch.Tensor:
+    """``C[M,N] = A B^T (+ residual)`` on the tcgen05 kernel.
+
+    ``a`` is ``(M, K)`` (``a_mn=False``) or ``(K, M)`` (``a_mn=True``); ``b`` is ``(N, K)`` or
+    ``(K, N)``. Both are 2-D bf16 with a contiguous last dim. ``residual`` has C's dtype and may be
+    ``out`` itself (in-place accumulation, used for fp32 weight-gradient accumulation).
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"inner dims differ: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=out_dtype)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    c_fp32 = 1 if out.dtype == torch.float32 else 0
+    if residual is not None:
+        assert residual.dtype == out.dtype and residual.shape == out.shape and residual.stride(1) == 1
+    _lib.call("ra_gemm_bf16", ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K,
+              c_ll(a.stride(0)), c_ll(b.stride(0)), c_ll(out.stride(0)),
+              c_ll(residual.stride(0) if residual is not None else 0),
+              int(a_mn), int(b_mn), c_fp32, group_m, _status(), stream_ptr())
+    return out
+
+
+def linear_fwd(x, w, out=None, residual=None):
+    """``y = x W^T (+ residual)``; ``x (M,K)``, ``w (N,K)``."""
+    return gemm(x, w, out=out, residual=residual)
+
+
+def linear_dgrad(dy, w, out=None, residual=None):
+    """``dx = dy W (+ residual)``; ``dy (M,N)``, ``w (N,K)`` read MN-major."""
+    return gemm(dy, w, b_mn=True, out=out, residual=residual)
+
+
+def linear_wgrad(dy, x, dw_acc):
+    """``dW += dy^T x`` accumulated in fp32; ``dy (M,N)``, ``x (M,K)``, ``dw_acc (N,K)`` fp32."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=dw_acc, residual=dw_acc)
+
+
+# ---------------------------------------------------------------------------------------------
+# normalisation / rope / activation
+# ---------------------------------------------------------------------------------------------
+def rmsnorm_fwd(x, w, eps: float, out=None, rstd=None):
+    rows, d = x.shape
+    assert x.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x)
+    if rstd is None:
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+    _lib.call("ra_rmsnorm_fwd", ptr(x), ptr(w), ptr(out), ptr(rstd), rows, d, c_f(eps), stream_ptr())
+    return out, rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dw_acc, dres=None, out=None):
+    """Returns ``dx (+ dres)``; adds the gain gradient to ``dw_acc`` (fp32)."""
+    rows, d = x.shape
+    assert dy.is_contiguous() and x.is_contiguous() and dw_acc.dtype == torch.float32
+    if out is None:
+        out = torch.empty_like(x)
+    _lib.call("ra_rmsnorm_bwd", ptr(dy), ptr(x), ptr(w), ptr(rstd), ptr(dres), ptr(out), ptr(dw_acc),
+              rows, d, stream_ptr())
+    return out
+
+
+def rope_(x, positions, theta: float, inverse: bool = False):
+    """Rotate a ``(B, S, H, D)`` bf16 view in place. ``positions`` is a flash.Positions map."""
+    B, S, H, D = x.shape
+    assert x.stride(3) == 1 and x.dtype == torch.bfloat16
+    _lib.call("ra_rope", ptr(x), c_ll(x.stride(0)), c_ll(x.stride(1)), c_ll(x.stride(2)), B, S, H, D,
+              int(positions.off0), int(positions.off1), int(min(positions.half, 1 << 30)), c_f(theta),
+              int(inverse), stream_ptr())
+    return x
+
+
+def swiglu_fwd(gu, out=None):
+    rows, f2 = gu.shape
+    F = f2 // 2
+    assert gu.is_contiguous()
+    if out is None:
+        out = torch.empty(rows, F, device=gu.device, dtype=torch.bfloat16)
+    _lib.call("ra_swiglu_fwd", ptr(gu), ptr(out), c_ll(rows), F, stream_ptr())
+    return out
+
+
+def swiglu_bwd_(gu, dh):
+    """Overwrites ``gu`` with ``[d gate | d up]``."""
+    rows, f2 = gu.shape
+    assert gu.is_contiguous() and dh.is_contiguous()
+    _lib.call("ra_swiglu_bwd", ptr(gu), ptr(dh), ptr(gu), c_ll(rows), f2 // 2, stream_ptr())
+    return gu
+
+
+# ---------------------------------------------------------------------------------------------
+# embedding / loss
+# ---------------------------------------------------------------------------------------------
+def embedding_fwd(tokens, table, out=None):
+    n = tokens.numel()
+    vocab, d = table.shape
+    assert tokens.dtype == torch.int32 and tokens.is_contiguous()
+    if out is None:
+        out = torch.empty(n, d, device=table.device, dtype=torch.bfloat16)
+    _lib.call("ra_embedding_fwd", ptr(tokens), ptr(table), ptr(out), c_ll(n), d, vocab, stream_ptr())
+    return out
+
+
+def embedding_bwd(tokens, dy, dtable_acc):
+    n = tokens.numel()
+    vocab, d = dtable_acc.shape
+    assert dtable_acc.dtype == torch.float32 and dy.is_contiguous()
+    _lib.call("ra_embedding_bwd", ptr(tokens), ptr(dy), ptr(dtable_acc), c_ll(n), d, vocab, stream_ptr())
+
+
+def xent_fwd_bwd_(logits, targets, grad_scale: float, loss=None):
+    """Per-row loss of a ``(rows, V)`` bf16 logits chunk; the logits are overwritten by
+    ``(softmax - onehot) * grad_scale``. Rows whose target is negative get zero loss and gradient."""
+    rows, V = logits.shape
+    assert logits.stride(1) == 1 and targets.dtype == torch.int32
+    if loss is None:
+        loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    _lib.call("ra_xent_fwd_bwd", ptr(logits), c_ll(logits.stride(0)), ptr(targets), ptr(loss),
+              c_ll(rows), V, c_f(grad_scale), stream_ptr())
+    return loss
+
+
+# ---------------------------------------------------------------------------------------------
+# optimizer / casts
+# ---------------------------------------------------------------------------------------------
+def sumsq(g, out):
+    """``out[0] += sum(g**2)`` for an fp32 buffer."""
+    assert g.dtype == torch.float32 and g.is_contiguous() and out.dtype == torch.float32
+    _lib.call("ra_sumsq", ptr(g), c_ll(g.numel()), ptr(out), stream_ptr())
+    return out
+
+
+def adamw_(p, m, v, g, p16, *, step: int, lr: float, beta1: float, beta2: float, eps: float,
+           weight_decay: float, decay_end: int, clip: float = 0.0, gnorm_sq=None, grad_mul: float = 1.0):
+    """One AdamW step over flat buffers (fp32 master/moments/grads, bf16 working copy)."""
+    n = p.numel()
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    _lib.call("ra_adamw", ptr(p), ptr(m), ptr(v), ptr(g), ptr(p16), c_ll(n), c_ll(decay_end),
+              c_f(lr), c_f(beta1), c_f(beta2), c_f(eps), c_f(weight_decay), c_f(bc1), c_f(bc2),
+              c_f(clip), ptr(gnorm_sq), c_f(grad_mul), stream_ptr())
+
+
+def cast_f32_to_bf16(src, dst):
+    """``src`` ``(rows, d)`` fp32 contiguous -> ``dst`` bf16 2-D view (row stride allowed)."""
+    rows, d = src.shape
+    assert src.is_contiguous() and dst.stride(1) == 1 and dst.shape == src.shape
+    _lib.call("ra_cast_f32_bf16", ptr(src), ptr(dst), c_ll(rows), d, c_ll(dst.stride(0)), stream_ptr())
+    return dst
+
+
+def cast_bf16_to_f32(src, dst):
+    assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
+    _lib.call("ra_cast_bf16_f32", ptr(src), ptr(dst), c_ll(src.numel()), stream_ptr())
+    return dst

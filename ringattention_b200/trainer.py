@@ -1,0 +1,229 @@
+"""Training engine: process-group / mesh bring-up, synthetic and packed-document data, the
+training step (H2D -> forward/backward -> gradient all-reduce -> clip + AdamW -> loss D2H),
+metrics and checkpoint/resume. One process drives one GPU.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .config import LlamaConfig, MeshConfig, TrainConfig
+from .models.llama import FlatParams, LlamaModel, StepContext
+from .ops import _lib
+from .ops import kernels as K
+from .ops.reference import shard_positions
+from .parallel.mesh import DeviceMesh
+
+
+def init_distributed(backend: Optional[str] = None) -> Tuple[int, int, int]:
+    """Initialise ``torch.distributed`` from the torchrun environment (no-op for one process).
+    Returns ``(rank, world_size, local_rank)``."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        be = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+        kwargs = {}
+        if be == "nccl":
+            kwargs["device_id"] = torch.device("cuda", local)
+        dist.init_process_group(backend=be, rank=rank, world_size=world, **kwargs)
+    return rank, world, local
+
+
+def geometric_segment_ids(batch: int, seq_len: int, mean_len: int, generator: torch.Generator) -> torch.Tensor:
+    """Packed documents: lengths ~ Geometric(1/mean_len), truncated to the sequence; returns
+    ``(batch, seq_len)`` int32 ids that increase along the sequence."""
+    p = 1.0 / float(mean_len)
+    boundary = torch.rand(batch, seq_len, generator=generator) < p
+    boundary[:, 0] = False
+    return torch.cumsum(boundary.to(torch.int32), dim=1).to(torch.int32)
+
+
+def synthetic_batch(cfg: LlamaConfig, batch: int, seq_len: int, generator: torch.Generator,
+                    mean_doc_len: int = 0):
+    """Uniform random tokens in ``[0, vocab)`` with next-token targets (the last position, and the
+    last token of every packed document, has target -1). CPU tensors."""
+    tokens = torch.randint(0, cfg.vocab_size, (batch, seq_len), generator=generator, dtype=torch.int32)
+    targets = torch.full_like(tokens, -1)
+    targets[:, :-1] = tokens[:, 1:]
+    seg = None
+    if mean_doc_len > 0:
+        seg = geometric_segment_ids(batch, seq_len, mean_doc_len, generator)
+        last = torch.ones_like(seg, dtype=torch.bool)
+        last[:, :-1] = seg[:, 1:] != seg[:, :-1]
+        targets[last] = -1
+    return tokens, targets, seg
+
+
+class Trainer:
+    """Owns the model replica of this rank and runs training steps on the mesh.
+
+    Mesh semantics: ``sp`` shards the sequence (ring attention), ``dp`` and ``fsdp`` shard the
+    batch; parameters are replicated over ``sp``/``dp``; over ``fsdp`` the optimizer state is
+    sharded (each rank updates its slice and the updated bf16 weights are all-gathered).
+    """
+
+    def __init__(self, model_cfg: LlamaConfig, train_cfg: TrainConfig, mesh: Optional[DeviceMesh] = None,
+                 device: Optional[torch.device] = None):
+        self.cfg = model_cfg
+        self.tc = train_cfg
+        self.rank, self.world, self.local_rank = init_distributed()
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.mesh = mesh or DeviceMesh(MeshConfig.parse(train_cfg.mesh))
+        self.sp_rank, self.sp = self.mesh.index("sp"), self.mesh.size("sp")
+        self.fsdp_rank, self.fsdp = self.mesh.index("fsdp"), self.mesh.size("fsdp")
+        self.dp_rank, self.dp = self.mesh.index("dp"), self.mesh.size("dp")
+        self.batch_groups = self.dp * self.fsdp
+        self.batch_index = self.dp_rank * self.fsdp + self.fsdp_rank
+        if train_cfg.global_batch % self.batch_groups:
+            raise ValueError("global_batch must be divisible by dp*fsdp")
+        if train_cfg.seq_len % self.sp:
+            raise ValueError("seq_len must be divisible by sp")
+        self.B = train_cfg.global_batch // self.batch_groups
+        self.S = train_cfg.seq_len // self.sp
+        params = FlatParams(model_cfg, self.device, seed=train_cfg.seed, with_optimizer=True,
+                            shard=(self.fsdp_rank, self.fsdp))
+        self.model = LlamaModel(model_cfg, self.device, params=params)
+        self.symm_ring = None
+        if self.sp > 1:
+            from .parallel.symm import SymmRing
+
+            self.symm_ring = SymmRing(self.mesh.axis("sp").group, self.device)
+            self.mesh.axis("sp").symm_ring = self.symm_ring
+        self.step_idx = 0
+        self.gnorm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
+        self.gen = torch.Generator()
+        self.gen.manual_seed(train_cfg.seed + 1)
+        # pinned staging for the per-step host->device input copy
+        n = self.B * self.S
+        self._tok_host = torch.empty(self.B, self.S, dtype=torch.int32).pin_memory()
+        self._tgt_host = torch.empty(self.B, self.S, dtype=torch.int32).pin_memory()
+        self._tok_dev = torch.empty(self.B, self.S, dtype=torch.int32, device=self.device)
+        self._tgt_dev = torch.empty(self.B, self.S, dtype=torch.int32, device=self.device)
+        self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        self._ctx_cache: Optional[StepContext] = None
+        self._ctx_seg_key = None
+
+    # ------------------------------------------------------------------ data
+    def make_global_batch(self):
+        """Synthetic global batch (identical on every rank: same generator seed)."""
+        return synthetic_batch(self.cfg, self.tc.global_batch, self.tc.seq_len, self.gen,
+                               self.tc.packed_mean_doc_len)
+
+    def shard_batch(self, tokens, targets):
+        """Slice this rank's rows (batch groups) and token positions (sp shard, layout-aware)."""
+        b0 = self.batch_index * self.B
+        pos = shard_positions(self.sp_rank, self.sp, self.S, self.cfg.layout)
+        return (tokens[b0:b0 + self.B].index_select(1, pos), targets[b0:b0 + self.B].index_select(1, pos))
+
+    def h2d_bytes_per_step(self) -> int:
+        return self._tok_host.numel() * 4 + self._tgt_host.numel() * 4
+
+    def d2h_bytes_per_step(self) -> int:
+        return 4
+
+    # ------------------------------------------------------------------ step
+    def context(self, segment_ids=None) -> StepContext:
+        key = None if segment_ids is None else (segment_ids.data_ptr(), tuple(segment_ids.shape))
+        if self._ctx_cache is None or key != self._ctx_seg_key or segment_ids is not None:
+            b0 = self.batch_index * self.B
+            seg = None if segment_ids is None else segment_ids[b0:b0 + self.B].to(self.device)
+            self._ctx_cache = self.model.make_context(
+                self.B, self.S, self.sp_rank, self.sp, segment_ids=seg, symm_ring=self.symm_ring,
+                total_tokens=self.tc.global_batch * self.tc.seq_len)
+            self._ctx_seg_key = key
+        return self._ctx_cache
+
+    def device_step(self, tok_dev, tgt_dev, ctx: StepContext) -> torch.Tensor:
+        """Forward/backward, gradient reduction and optimizer update on device-resident inputs.
+        Returns the global mean loss as a 0-d device tensor."""
+        P = self.model.params
+        P.ensure_grads().zero_()
+        loss_sum = self.model.forward_backward(tok_dev, tgt_dev, ctx)
+        if self.world > 1:
+            dist.all_reduce(loss_sum)
+            self._all_reduce_grads()
+        self.optimizer_step()
+        return loss_sum / max(1, ctx.total_tokens)
+
+    def _all_reduce_grads(self, bucket: int = 1 << 28) -> None:
+        g = self.model.params.g32
+        for s0 in range(0, g.numel(), bucket):
+            dist.all_reduce(g[s0:s0 + bucket])
+
+    def optimizer_step(self) -> None:
+        P, tc = self.model.params, self.tc
+        self.step_idx += 1
+        lo, hi = P.shard_range()
+        clip = float(tc.grad_clip)
+        if clip > 0:
+            self.gnorm_sq.zero_()
+            K.sumsq(P.g32, self.gnorm_sq)
+        decay_end = max(0, min(P.decay_end, hi) - lo)
+        K.adamw_(P.p32, P.m, P.v, P.g32[lo:hi], P.p16[lo:hi], step=self.step_idx, lr=tc.lr,
+                 beta1=tc.beta1, beta2=tc.beta2, eps=tc.eps, weight_decay=tc.weight_decay,
+                 decay_end=decay_end, clip=clip, gnorm_sq=self.gnorm_sq if clip > 0 else None)
+        if self.fsdp > 1:
+            group = self.mesh.axis("fsdp").group
+            dist.all_gather_into_tensor(P.p16, P.p16[lo:hi].clone(), group=group)
+
+    def train_step(self, tokens_cpu, targets_cpu, segment_ids=None) -> float:
+        """The end-to-end step a user calls: sharded inputs come from pinned host memory, the loss
+        comes back to the host."""
+        tok, tgt = self.shard_batch(tokens_cpu, targets_cpu)
+        self._tok_host.copy_(tok)
+        self._tgt_host.copy_(tgt)
+        self._tok_dev.copy_(self._tok_host, non_blocking=True)
+        self._tgt_dev.copy_(self._tgt_host, non_blocking=True)
+        ctx = self.context(segment_ids)
+        loss = self.device_step(self._tok_dev, self._tgt_dev, ctx)
+        self._loss_host.copy_(loss.reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        _lib.check_status(self.device)
+        return float(self._loss_host[0])
+
+    # ------------------------------------------------------------------ metrics
+    def model_flops_per_step(self) -> float:
+        return self.model.flops_per_token(self.tc.seq_len) * self.tc.global_batch * self.tc.seq_len
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def save_checkpoint(self, directory: str) -> str:
+        """Each rank writes its optimizer shard; rank 0 of every parameter replica set also writes
+        the metadata. Files: ``rank{r}.pt`` and ``meta.json``."""
+        os.makedirs(directory, exist_ok=True)
+        P = self.model.params
+        path = os.path.join(directory, f"rank{self.rank}.pt")
+        torch.save({"p32": P.p32.cpu(), "m": P.m.cpu(), "v": P.v.cpu(), "step": self.step_idx,
+                    "gen": self.gen.get_state(), "shard": (P.shard_index, P.shard_count)}, path)
+        if self.rank == 0:
+            with open(os.path.join(directory, "meta.json"), "w") as f:
+                json.dump({"step": self.step_idx, "world": self.world, "mesh": self.mesh.config.shape(),
+                           "model": self.cfg.__dict__, "train": self.tc.asdict()}, f, default=str)
+        if self.world > 1:
+            dist.barrier()
+        return path
+
+    def load_checkpoint(self, directory: str) -> None:
+        P = self.model.params
+        st = torch.load(os.path.join(directory, f"rank{self.rank}.pt"), map_location="cpu")
+        if tuple(st["shard"]) != (P.shard_index, P.shard_count):
+            raise ValueError("checkpoint was written with a different fsdp sharding")
+        P.p32.copy_(st["p32"])
+        P.m.copy_(st["m"])
+        P.v.copy_(st["v"])
+        self.step_idx = int(st["step"])
+        self.gen.set_state(st["gen"])
+        lo, hi = P.shard_range()
+        P.p16[lo:hi].copy_(P.p32)
+        if self.fsdp > 1:
+            dist.all_gather_into_tensor(P.p16, P.p16[lo:hi].clone(), group=self.mesh.axis("fsdp").group)
