@@ -1,5 +1,5 @@
-// Thin inline-PTX layer for Blackwell (sm_100a): mbarrier, TMA (cp.async.bulk.tensor, never with
-// cluster multicast), tcgen05 tensor-core MMA with TMEM accumulators, and bounded waits.
+// Thin inline-PTX layer for Blackwell (sm_100a): mbarrier, TMA (cp.async.bulk.tensor, always to
+// one destination CTA), tcgen05 tensor-core MMA with TMEM accumulators, and bounded waits.
 //
 // Every wait in this library is bounded: when a deadline passes the waiting thread records a
 // status code in global memory, raises a CTA-wide abort flag in shared memory and returns false;
@@ -111,7 +111,7 @@ __device__ __forceinline__ void bounded_drain_pause() {
 }
 
 // ----------------------------------------------------------------------------------------------
-// TMA (tiled bulk tensor copies). No multicast qualifier is ever used.
+// TMA (tiled bulk tensor copies), each issued by and for one CTA.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

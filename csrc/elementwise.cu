@@ -386,17 +386,17 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
 }
 
 // ---------------------------------------------------------------------------------- casts
-// fp32 (rows, d) contiguous -> bf16 view with a row stride (used for dQ into a fused dQKV buffer).
+// fp32 (rows, d) with a row stride -> bf16 view with a row stride (used for dQ into a fused dQKV buffer).
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
-                                     long long rows, int d, long long dst_ld) {
+                                     long long rows, int d, long long src_ld, long long dst_ld) {
   const int nv = d >> 3;
   const long long total = rows * nv;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = idx / nv;
     const int v = static_cast<int>(idx - r * nv);
-    const float4 a = reinterpret_cast<const float4*>(src + r * d)[2 * v];
-    const float4 b = reinterpret_cast<const float4*>(src + r * d)[2 * v + 1];
+    const float4 a = reinterpret_cast<const float4*>(src + r * src_ld)[2 * v];
+    const float4 b = reinterpret_cast<const float4*>(src + r * src_ld)[2 * v + 1];
     const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     *reinterpret_cast<uint4*>(dst + r * dst_ld + v * 8) = pack8(f);
   }
@@ -525,11 +525,11 @@ extern "C" int ra_adamw(float* p, float* m, float* v, const float* g, void* p16,
   return check_launch("adamw");
 }
 
-extern "C" int ra_cast_f32_bf16(const float* src, void* dst, long long rows, int d, long long dst_ld,
-                                void* stream) {
-  if (d % 8 || dst_ld % 8) { set_error("cast: d must be a multiple of 8"); return kHostBadArg; }
+extern "C" int ra_cast_f32_bf16(const float* src, void* dst, long long rows, int d, long long src_ld,
+                                long long dst_ld, void* stream) {
+  if (d % 8 || dst_ld % 8 || src_ld % 4) { set_error("cast: d must be a multiple of 8"); return kHostBadArg; }
   cast_f32_bf16_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      src, static_cast<bf16*>(dst), rows, d, dst_ld);
+      src, static_cast<bf16*>(dst), rows, d, src_ld, dst_ld);
   return check_launch("cast_f32_bf16");
 }
 extern "C" int ra_cast_bf16_f32(const void* src, float* dst, long long n, void* stream) {

@@ -180,10 +180,11 @@ def adamw_(p, m, v, g, p16, *, step: int, lr: float, beta1: float, beta2: float,
 
 
 def cast_f32_to_bf16(src, dst):
-    """``src`` ``(rows, d)`` fp32 contiguous -> ``dst`` bf16 2-D view (row stride allowed)."""
+    """``src`` ``(rows, d)`` fp32 -> ``dst`` bf16; both 2-D views, row strides allowed."""
     rows, d = src.shape
-    assert src.is_contiguous() and dst.stride(1) == 1 and dst.shape == src.shape
-    _lib.call("ra_cast_f32_bf16", ptr(src), ptr(dst), c_ll(rows), d, c_ll(dst.stride(0)), stream_ptr())
+    assert src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape == src.shape
+    _lib.call("ra_cast_f32_bf16", ptr(src), ptr(dst), c_ll(rows), d, c_ll(src.stride(0)),
+              c_ll(dst.stride(0)), stream_ptr())
     return dst
 
 
