@@ -86,6 +86,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   using SM = BwdSmem<D>;
   constexpr int NSLAB = D / 64;
 
+  // A failure recorded earlier on this stream (for example a ring barrier that timed out) turns
+  // every later attention kernel into a no-op, so nothing touches the memory of a lost peer.
+  if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
+
   if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
     const long long stride = static_cast<long long>(p.copy_ctas) * BWD_THREADS;
     long long i = static_cast<long long>(blockIdx.x) * BWD_THREADS + threadIdx.x;

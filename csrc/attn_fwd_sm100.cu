@@ -60,6 +60,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   using SM = FwdSmem<D>;
   constexpr int NSLAB = D / 64;
 
+  // A failure recorded earlier on this stream (for example a ring barrier that timed out) turns
+  // every later attention kernel into a no-op, so nothing touches the memory of a lost peer.
+  if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
+
   // ------------------------------------------------------------ copy CTAs (ring KV pull)
   if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
     const long long stride = static_cast<long long>(p.copy_ctas) * FWD_THREADS;

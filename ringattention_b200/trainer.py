@@ -65,6 +65,10 @@ def synthetic_batch(cfg: LlamaConfig, batch: int, seq_len: int, generator: torch
     return tokens, targets, seg
 
 
+class PeerLost(RuntimeError):
+    """Another rank announced that it left the job; nothing was launched for this step."""
+
+
 class Trainer:
     """Owns the model replica of this rank and runs training steps on the mesh.
 
@@ -177,9 +181,33 @@ class Trainer:
             group = self.mesh.axis("fsdp").group
             dist.all_gather_into_tensor(P.p16, P.p16[lo:hi].clone(), group=group)
 
+    # ------------------------------------------------------------------ failure detection (host side)
+    def _store(self):
+        if self.world == 1:
+            return None
+        from torch.distributed import distributed_c10d as c10d
+
+        return c10d._get_default_store()
+
+    def leave(self) -> None:
+        """Announce that this rank stops taking part (call between steps, nothing in flight)."""
+        torch.cuda.synchronize(self.device)
+        st = self._store()
+        if st is not None:
+            st.add("ringattn_b200/left", 1)
+
+    def check_peers(self) -> None:
+        """Raise :class:`PeerLost` before launching anything if a peer has left. Kernels that touch
+        peer memory are only launched after this check; a peer that dies without announcing it is
+        caught by the bounded ring barrier (status word) or the process-group timeout."""
+        st = self._store()
+        if st is not None and st.add("ringattn_b200/left", 0) > 0:
+            raise PeerLost(f"rank {self.rank}: a peer left the job; step {self.step_idx + 1} not launched")
+
     def train_step(self, tokens_cpu, targets_cpu, segment_ids=None) -> float:
         """The end-to-end step a user calls: sharded inputs come from pinned host memory, the loss
         comes back to the host."""
+        self.check_peers()
         tok, tgt = self.shard_batch(tokens_cpu, targets_cpu)
         self._tok_host.copy_(tok)
         self._tgt_host.copy_(tgt)

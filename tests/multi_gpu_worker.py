@@ -1,0 +1,95 @@
+"""Worker run under torchrun by test_gpu_multi.py (one process per GPU, NVLS off)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ringattention_b200 import ringattention  # noqa: E402
+from ringattention_b200.config import LlamaConfig, TrainConfig  # noqa: E402
+from ringattention_b200.ops import _lib, reference as R  # noqa: E402
+from ringattention_b200.trainer import PeerLost, Trainer, init_distributed  # noqa: E402
+
+
+def ring_vs_dense(rank, world, dev):
+    ok = True
+    B, H, D, Sl = 1, 4, 128, 512
+    S = Sl * world
+    for layout in ("contiguous", "zigzag"):
+        for cbs, seg in ((1, False), (None, True)):
+            torch.manual_seed(0)
+            q, k, v, do = [torch.randn(B, S, H, D, device=dev).bfloat16() for _ in range(4)]
+            for t in (q, k, v, do):
+                dist.broadcast(t, 0)
+            ids = None
+            if seg:
+                ids = torch.cumsum((torch.rand(B, S, device=dev) < 0.004).int(), 1).int()
+                dist.broadcast(ids, 0)
+            pos = R.shard_positions(rank, world, Sl, layout, dev)
+            ql, kl, vl = [t.index_select(1, pos).contiguous().requires_grad_(True) for t in (q, k, v)]
+            kw = dict(causal_block_size=cbs, query_chunk_size=128, key_chunk_size=128, layout=layout)
+            out = ringattention(ql, kl, vl, None, ids, None, "sp", True, kw)
+            out.backward(do.index_select(1, pos).contiguous())
+            torch.cuda.synchronize()
+            _lib.check_status()
+            qf, kf, vf = [t.float().requires_grad_(True) for t in (q, k, v)]
+            ref = R.dense_attention(qf, kf, vf, causal_block_size=cbs, seg_q=ids, seg_k=ids, dtype=torch.float32)
+            ref.backward(do.float())
+            e = (out.float() - ref.detach().index_select(1, pos)).abs().max().item()
+            rel = lambda a, b: ((a.float() - b).abs().max() / (b.abs().max() + 1e-9)).item()
+            g = max(rel(ql.grad, qf.grad.index_select(1, pos)), rel(kl.grad, kf.grad.index_select(1, pos)),
+                    rel(vl.grad, vf.grad.index_select(1, pos)))
+            ok &= e < 0.03 and g < 0.03
+            print(f"[{rank}] ring {layout} cbs={cbs} seg={seg}: out {e:.4f} grad {g:.4f}", flush=True)
+    return ok
+
+
+def trainer_parity_and_peer_loss(rank, world, dev):
+    cfg = LlamaConfig.named("llama-tiny", layout="zigzag")
+    tc = TrainConfig(model="llama-tiny", mesh=f"1,1,1,{world}", seq_len=512 * world, global_batch=1, lr=1e-3, seed=11)
+    tr = Trainer(cfg, tc)
+    tokens, targets, seg = tr.make_global_batch()
+    l_sp = tr.train_step(tokens, targets, seg)
+    # same batch on one device (every rank computes it redundantly; only the loss is compared)
+    from ringattention_b200.models.llama import LlamaModel
+    ref_model = LlamaModel(LlamaConfig.named("llama-tiny"), dev, seed=11, with_optimizer=False)
+    ctx = ref_model.make_context(1, 512 * world)
+    l_ref = ref_model.forward_loss(tokens.to(dev), targets.to(dev), ctx).item() / (512 * world)
+    ok = abs(l_sp - l_ref) < 2e-2
+    print(f"[{rank}] trainer sp={world} loss {l_sp:.4f} vs single-device {l_ref:.4f}", flush=True)
+    l2 = tr.train_step(tokens, targets, seg)
+    ok &= l2 < l_sp
+    # a rank leaves between steps; the others find out on the host before launching anything
+    dist.barrier()
+    if rank == world - 1:
+        tr.leave()
+        print(f"[{rank}] left", flush=True)
+        return ok, True
+    import time
+    time.sleep(1.0)
+    try:
+        tr.train_step(tokens, targets, seg)
+        ok = False
+        print(f"[{rank}] peer loss NOT detected", flush=True)
+    except PeerLost as e:
+        print(f"[{rank}] detected: {e}", flush=True)
+    ok &= float((torch.ones(4, device=dev) * 3).sum()) == 12.0  # context still usable
+    return ok, False
+
+
+def main():
+    rank, world, local = init_distributed()
+    dev = torch.device("cuda", local)
+    from ringattention_b200.parallel.mesh import DeviceMesh
+
+    DeviceMesh(f"1,1,1,{world}")
+    ok = ring_vs_dense(rank, world, dev)
+    ok2, left = trainer_parity_and_peer_loss(rank, world, dev)
+    print(f"[{rank}] RESULT {'OK' if (ok and ok2) else 'FAIL'}", flush=True)
+    os._exit(0 if (ok and ok2) else 1)
+
+
+if __name__ == "__main__":
+    main()

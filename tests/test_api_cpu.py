@@ -1,0 +1,219 @@
+"""CPU tests of the public API surface: kwargs parsing, mesh, blockwise FFN, dispatch, comm faults."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+import ringattention_b200 as rab
+from ringattention_b200.config import BlockwiseKwargs, LlamaConfig, MeshConfig
+from ringattention_b200.ops import reference as R
+from ringattention_b200.parallel import mesh as M
+from ringattention_b200.parallel.comm import FakeRing, RingTimeout, SingleComm, run_fake_ring
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_public_names():
+    for n in ("ringattention", "blockwise_feedforward", "ringattention_inference", "ringattention_jax"):
+        assert callable(getattr(rab, n))
+
+
+def test_blockwise_kwargs_accepts_reference_dict():
+    ref_dict = dict(causal_block_size=1, deterministic=True, dropout_rng=None, attn_pdrop=0.0,
+                    query_chunk_size=512, key_chunk_size=512, dtype=torch.float32,
+                    policy="nothing_saveable", precision=None, prevent_cse=True)
+    kw = BlockwiseKwargs.from_any(ref_dict)
+    assert kw.causal_block_size == 1 and kw.query_chunk_size == 512 and not kw.dropout_active
+    with pytest.raises(KeyError):
+        BlockwiseKwargs.from_any({"chunk": 3})
+    with pytest.raises(ValueError):
+        BlockwiseKwargs.from_any({"attn_pdrop": 1.5})
+
+    def nothing_saveable():  # a policy given as a function object, as jax users do
+        pass
+
+    assert BlockwiseKwargs.from_any({"policy": nothing_saveable}).policy == "nothing_saveable"
+
+
+def test_mesh_config_parse_and_coords():
+    m = MeshConfig.parse("1,2,1,4")
+    assert (m.dp, m.fsdp, m.tp, m.sp) == (1, 2, 1, 4) and m.world_size == 8
+    assert MeshConfig.parse("fsdp=2,sp=4").shape() == (1, 2, 1, 4)
+    with pytest.raises(ValueError):
+        MeshConfig.parse("2,2")
+    dm = M.DeviceMesh("1,1,1,1", register=False)
+    assert dm.coords == (0, 0, 0, 0) and dm.size("sp") == 1
+
+
+def test_ringattention_single_device_cpu_matches_dense():
+    g = torch.Generator().manual_seed(0)
+    q, k, v = [torch.randn(2, 64, 2, 16, generator=g, requires_grad=True) for _ in range(3)]
+    out = rab.ringattention(q, k, v, None, None, None, None, True,
+                            dict(causal_block_size=1, query_chunk_size=16, key_chunk_size=16))
+    ref = R.dense_attention(q, k, v, causal_block_size=1, dtype=torch.float32)
+    assert torch.allclose(out, ref, atol=1e-5)
+    out.sum().backward()
+    assert q.grad is not None and k.grad is not None and v.grad is not None
+
+
+def test_axis_registry_with_fake_ring():
+    g = torch.Generator().manual_seed(1)
+    q, k, v = [torch.randn(1, 64, 2, 8, generator=g, dtype=torch.float64) for _ in range(3)]
+
+    def body(comm):
+        M.register_axis("sp", comm, thread_local=True)
+        sl = slice(comm.rank * 32, (comm.rank + 1) * 32)
+        return rab.ringattention(q[:, sl], k[:, sl], v[:, sl], axis_name="sp",
+                                 blockwise_kwargs=dict(causal_block_size=1, query_chunk_size=16,
+                                                       key_chunk_size=16))
+
+    outs = run_fake_ring(2, body)
+    ref = R.dense_attention(q, k, v, causal_block_size=1)
+    assert torch.allclose(torch.cat(outs, 1), ref, atol=1e-10)
+    with pytest.raises(KeyError):
+        M.resolve_axis("nope")
+
+
+def test_blockwise_feedforward_equals_unchunked_with_grads():
+    torch.manual_seed(0)
+    ffn = torch.nn.Sequential(torch.nn.Linear(16, 64), torch.nn.SiLU(), torch.nn.Linear(64, 16)).double()
+    x = torch.randn(2, 48, 16, dtype=torch.float64, requires_grad=True)
+    y_ref = ffn(x)
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    gx_ref = x.grad.clone()
+    gw_ref = [p.grad.clone() for p in ffn.parameters()]
+    for pre_remat in (True, False):
+        x.grad = None
+        ffn.zero_grad()
+        y = rab.blockwise_feedforward(ffn, x, 12, pre_remat=pre_remat)
+        assert torch.allclose(y, y_ref, atol=1e-12)
+        y.backward(g)
+        assert torch.allclose(x.grad, gx_ref, atol=1e-12)
+        for p, r in zip(ffn.parameters(), gw_ref):
+            assert torch.allclose(p.grad, r, atol=1e-12)
+    with pytest.raises(ValueError):
+        rab.blockwise_feedforward(ffn, x, 7)
+
+
+def test_fake_ring_dropped_message_times_out():
+    comms = FakeRing.create(2, timeout=0.3)
+    comms[0].drop_next_message_to(1)
+    errs = []
+
+    def body(comm):
+        try:
+            comm.send_recv([torch.zeros(1)])
+        except RingTimeout as e:
+            errs.append((comm.rank, str(e)))
+            raise
+
+    import threading
+    ts = [threading.Thread(target=lambda c=c: _swallow(body, c)) for c in comms]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert any(r == 1 for r, _ in errs)
+
+
+def _swallow(fn, c):
+    try:
+        fn(c)
+    except RingTimeout:
+        pass
+
+
+def test_fake_ring_rank_failure_propagates():
+    def body(comm):
+        if comm.rank == 1:
+            raise RuntimeError("rank 1 died before the ring step")
+        comm.barrier()
+        return 0
+
+    with pytest.raises((RuntimeError, RingTimeout)):
+        run_fake_ring(3, body, timeout=1.0)
+
+
+_GLOO_SCRIPT = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    from ringattention_b200.parallel.mesh import DeviceMesh
+    from ringattention_b200.ops import reference as R
+    import ringattention_b200 as rab
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mesh = DeviceMesh(f"1,1,1,{{world}}")
+    g = torch.Generator().manual_seed(0)
+    B, S, H, D = 1, 2048, 8, 64
+    q, k, v, do = [torch.randn(B, S, H, D, generator=g) for _ in range(4)]
+    sl = slice(rank * (S // world), (rank + 1) * (S // world))
+    ql, kl, vl = [t[:, sl].clone().requires_grad_(True) for t in (q, k, v)]
+    kw = dict(causal_block_size=1, query_chunk_size=256, key_chunk_size=256, deterministic=True,
+              dropout_rng=None, attn_pdrop=0.0, dtype=torch.float32, policy="nothing_saveable",
+              precision=None, prevent_cse=True)
+    out = rab.ringattention(ql, kl, vl, torch.zeros(B, 1, 1, S), torch.zeros(B, S, dtype=torch.int32),
+                            None, "sp", True, kw)
+    (out * do[:, sl]).sum().backward()
+    qa, ka, va = [t.double().requires_grad_(True) for t in (q, k, v)]
+    ref = R.dense_attention(qa, ka, va, causal_block_size=1)
+    (ref * do.double()).sum().backward()
+    ok = torch.allclose(out.double(), ref.detach()[:, sl], atol=2e-4)
+    ok &= torch.allclose(ql.grad.double(), qa.grad[:, sl], atol=1e-3)
+    ok &= torch.allclose(kl.grad.double(), ka.grad[:, sl], atol=1e-3)
+    ok &= torch.allclose(vl.grad.double(), va.grad[:, sl], atol=1e-3)
+    print("RANK", rank, "OK" if ok else "FAIL", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+""")
+
+
+def test_cpu_plumbing_four_gloo_processes(tmp_path):
+    """The CPU plumbing config as four real processes over gloo (isend/irecv rotation)."""
+    script = tmp_path / "gloo_ring.py"
+    script.write_text(_GLOO_SCRIPT.format(repo=REPO))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                        "--master-addr", "127.0.0.1", "--master-port", "29617", str(script)],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert p.stdout.count("OK") == 4
+
+
+_GLOO_FAIL_SCRIPT = textwrap.dedent("""
+    import os, sys, datetime, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    from ringattention_b200.parallel.comm import TorchDistRing
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=5))
+    rank = dist.get_rank()
+    ring = TorchDistRing()
+    ring.send_recv([torch.ones(4) * rank])          # a healthy step
+    if rank == 1:
+        os._exit(0)                                 # leaves between steps, nothing in flight
+    try:
+        ring.send_recv([torch.ones(4)])
+        print("NO ERROR", flush=True)
+        code = 1
+    except Exception as e:
+        print("DETECTED", type(e).__name__, flush=True)
+        code = 0
+    os._exit(code)
+""")
+
+
+def test_gloo_peer_exit_is_detected(tmp_path):
+    """A rank that leaves between steps makes its neighbour's next hop fail instead of hanging."""
+    script = tmp_path / "gloo_fail.py"
+    script.write_text(_GLOO_FAIL_SCRIPT.format(repo=REPO))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29631", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert "DETECTED" in outs[0], outs[0][-1500:]
+
+
+def test_llama_config_param_count():
+    cfg = LlamaConfig.named("llama-7b")
+    assert abs(cfg.n_params() - 6.74e9) / 6.74e9 < 0.01
+    assert cfg.head_dim == 128
