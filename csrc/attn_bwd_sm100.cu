@@ -17,6 +17,7 @@
 //   warp 1       tcgen05.mma issuer
 //   warps 2-9    softmax/dS group: two warps per TMEM lane quadrant, 64 q-columns each
 //   warps 10-13  dQ drain group: tcgen05.ld + red.global.add.v4.f32
+#include "attn_api.h"
 #include "attn_common.cuh"
 #include "common/host_util.h"
 
@@ -553,27 +554,6 @@ int make_bshd_map_bwd(CUtensorMap* m, const void* base, int B, int S, int H, int
 }
 }  // namespace
 
-struct RaAttnBwdArgs {
-  const void* q; const void* k; const void* v; const void* d_o;
-  long long q_sb, q_ss, q_sh;
-  long long k_sb, k_ss, k_sh;
-  long long v_sb, v_ss, v_sh;
-  long long do_sb, do_ss, do_sh;
-  const float* lse2; const float* delta; int Sq_pad;
-  float* dq_acc;
-  void* dk; void* dv; long long dkv_sb, dkv_ss, dkv_sh; int dkv_mode;
-  int B, H, Sq, Sk, D;
-  float softmax_scale;
-  int causal_block_size;
-  int q_off0, q_off1, q_half;
-  int k_off0, k_off1, k_half;
-  const int* seg_q; const int* seg_k; const int* seg_q_mm; const int* seg_k_mm;
-  const float* bias; long long bias_sb, bias_sh;
-  unsigned long long seed; unsigned int drop_threshold;
-  const void* copy_src; void* copy_dst; long long copy_bytes; int copy_ctas;
-  int* status;
-  void* stream;
-};
 
 extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   using namespace ra;
