@@ -17,6 +17,8 @@
 //   warp 1       tcgen05.mma issuer
 //   warps 2-9    softmax/dS group: two warps per TMEM lane quadrant, 64 q-columns each
 //   warps 10-13  dQ drain group: tcgen05.ld + red.global.add.v4.f32
+#include <stdlib.h>
+
 #include "attn_api.h"
 #include "attn_common.cuh"
 #include "common/host_util.h"
@@ -43,6 +45,7 @@ struct BwdParams {
   long long copy_n16;
   int copy_ctas;
   int* status;
+  int debug;
 };
 
 template <int D>
@@ -364,7 +367,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         for (int e = 0; e < 32; ++e) {
           const int col = half * 64 + c * 32 + e;
           float x = fmaf(__uint_as_float(s[e]), p.scale_log2, my_bias2) - lse2[col];
-          float pr = exp2_approx(x);
+          float pr = (p.debug & 4) ? x : exp2_approx(x);
           if (!plain) {
             bool masked = col < lo;
             if (mk.seg_q) masked |= (sSegQ[st * 128 + col] != my_seg);
@@ -477,7 +480,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         uint32_t r[32];
         tmem_ld_x32(tDP + lane_base + c * 32, r);
         tmem_ld_wait();
-        if (qi < mk.Sq) {
+        if (qi < mk.Sq && !(p.debug & 1)) {
 #pragma unroll
           for (int g = 0; g < 8; ++g)
             red_add_v4(dst + c * 32 + 4 * g, __uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
@@ -610,6 +613,7 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   p.copy_n16 = a->copy_bytes / 16;
   p.copy_ctas = (a->copy_src && a->copy_bytes > 0) ? a->copy_ctas : 0;
   p.status = a->status;
+  { const char* e = getenv("RINGATTN_B200_BWD_DEBUG"); p.debug = e ? atoi(e) : 0; }
   const int nkt = (a->Sk + 127) / 128;
   const long long grid = static_cast<long long>(nkt) * a->H * a->B + p.copy_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);

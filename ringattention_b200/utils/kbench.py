@@ -1,0 +1,134 @@
+"""Kernel micro-benchmarks with CUDA-event timing and roofline fractions.
+
+    python -m ringattention_b200.utils.kbench --kernel attn_fwd --seq 32768 --heads 32
+    python -m ringattention_b200.utils.kbench --kernel attn_bwd --seq 16384 --heads 16 --iters 1 --warmup 1
+    python -m ringattention_b200.utils.kbench --kernel gemm --m 65536 --n 4096 --k 4096
+
+Timing: ``--warmup`` untimed launches (>= 3 by default), then ``--iters`` launches between two CUDA
+events on the launching stream with a synchronize on both sides. The operands of the attention
+cases are far larger than the 126 MB L2 at the default sizes; ``--flush-l2`` writes a 256 MB buffer
+between iterations (then every iteration is timed on its own and the mean is reported).
+The denominators come from ``MEASURED_PEAKS.json`` at the repository root when present (fractions
+"of measured"), else 1590 TFLOP/s and 6650 GB/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..ops import _lib, flash
+from ..ops import kernels as K
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, 6650.0, "fallback"
+
+
+def time_launches(fn, warmup: int, iters: int, flush_l2: bool) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if not flush_l2:
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+    junk = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    total = 0.0
+    for _ in range(iters):
+        junk.fill_(1)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad"])
+    ap.add_argument("--seq", type=int, default=32768)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--causal", type=int, default=1)
+    ap.add_argument("--m", type=int, default=65536)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--flush-l2", action="store_true")
+    args = ap.parse_args(argv)
+    peak_tf, peak_gbs, how = peaks()
+    torch.manual_seed(0)
+    dev = "cuda"
+    res = {"kernel": args.kernel, "denominator": how}
+    if args.kernel.startswith("attn"):
+        B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
+        q = torch.randn(B, S, H, D, device=dev).bfloat16()
+        k, v, do = torch.randn_like(q), torch.randn_like(q), torch.randn_like(q)
+        ms = flash.MaskSpec(causal_block_size=args.causal, q_pos=flash.Positions(0), k_pos=flash.Positions(0))
+        out = torch.empty_like(q)
+        lse = torch.empty(B, H, S, device=dev)
+        frac = 0.5 if args.causal else 1.0
+        if args.kernel == "attn_fwd":
+            fn = lambda: flash.flash_fwd(q, k, v, ms, out=out, lse_out=lse)
+            flops = 4.0 * B * S * S * H * D * frac
+            bytes_ = 4.0 * q.numel() * 2
+        else:
+            flash.flash_fwd(q, k, v, ms, out=out, lse_out=lse)
+            lse2, delta = flash.flash_bwd_prep(out, do, lse)
+            dq_acc = torch.zeros(B, S, H, D, device=dev)
+            dk, dv = torch.empty_like(q), torch.empty_like(q)
+            fn = lambda: flash.flash_bwd(q, k, v, do, lse2, delta, ms, dq_acc, dk, dv)
+            flops = 10.0 * B * S * S * H * D * frac
+            bytes_ = 6.0 * q.numel() * 2 + q.numel() * 4
+        res.update(shape=[B, S, H, D], causal=args.causal)
+    else:
+        M, N, Kd = args.m, args.n, args.k
+        if args.kernel == "gemm":
+            a = torch.randn(M, Kd, device=dev).bfloat16()
+            b = torch.randn(N, Kd, device=dev).bfloat16()
+            c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            fn = lambda: K.gemm(a, b, out=c)
+        elif args.kernel == "gemm_dgrad":  # dx[M,N] = dy[M,K] W[K,N]
+            a = torch.randn(M, Kd, device=dev).bfloat16()
+            b = torch.randn(Kd, N, device=dev).bfloat16()
+            c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            fn = lambda: K.gemm(a, b, b_mn=True, out=c)
+        else:  # dW[M,N] += dy[K,M]^T x[K,N], fp32 accumulate
+            a = torch.randn(Kd, M, device=dev).bfloat16()
+            b = torch.randn(Kd, N, device=dev).bfloat16()
+            c = torch.zeros(M, N, device=dev, dtype=torch.float32)
+            fn = lambda: K.gemm(a, b, a_mn=True, b_mn=True, out=c, residual=c)
+        flops = 2.0 * M * N * Kd
+        bytes_ = 2.0 * (M * Kd + N * Kd) + c.element_size() * M * N
+        res.update(shape=[M, N, Kd])
+    ms_t = time_launches(fn, args.warmup, args.iters, args.flush_l2)
+    _lib.check_status()
+    tf = flops / ms_t / 1e9
+    res.update(ms=round(ms_t, 4), tflops=round(tf, 1), frac_of_bf16_peak=round(tf / peak_tf, 3),
+               algorithmic_gb=round(bytes_ / 1e9, 3), gbs=round(bytes_ / ms_t / 1e6, 1),
+               frac_of_hbm_peak=round(bytes_ / ms_t / 1e6 / peak_gbs, 3), iters=args.iters,
+               warmup=args.warmup, flush_l2=args.flush_l2)
+    print(json.dumps(res))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
