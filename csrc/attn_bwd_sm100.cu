@@ -5,7 +5,8 @@
 //     S^T  = K Q_i^T            (SS)  -> TMEM [0,128)
 //     dP^T = V dO_i^T           (SS)  -> TMEM [128,256)
 //     P^T  = exp2(S^T*c - lse)        -> packed bf16 over S^T (TMEM)
-//     dS^T = P^T (dP^T - delta) / sqrt(D)  -> bf16 in shared memory (128-byte swizzle)
+//     dS^T = P^T (dP^T - delta)       -> bf16 in shared memory (128-byte swizzle); the 1/sqrt(D)
+//                                        factor is applied when dQ and dK leave TMEM
 //     dV  += P^T dO_i           (A from TMEM)        -> TMEM [256,256+D)
 //     dK  += dS^T Q_i           (A = dS^T, K-major)  -> TMEM [384,384+D)
 //     dQ_i = dS K               (A = dS^T read MN-major, B = K MN-major) -> TMEM over dP^T
@@ -13,12 +14,10 @@
 // bf16, fp32 or as fp32 reductions into (possibly a peer GPU's) accumulators, which is how the
 // ring backward returns gradients to the owner of the KV block.
 //
-//   warp 0       TMA producer (K,V once; Q_i + lse/delta double-buffered; dO_i)
-//   warp 1       tcgen05.mma issuer
-//   warps 2-9    softmax/dS group: two warps per TMEM lane quadrant, 64 q-columns each
-//   warps 10-13  dQ drain group: tcgen05.ld + red.global.add.v4.f32
-#include <stdlib.h>
-
+//   warps 0-3    producer group (registers trimmed): warp 0 TMA (K,V once; Q_i + lse/delta
+//                double-buffered; dO_i), warp 1 tcgen05.mma issuer
+//   warps 4-11   softmax/dS group: two warps per TMEM lane quadrant, 64 q-columns each
+//   warps 12-15  dQ drain group (registers raised): tcgen05.ld, early release, red.global.add.v4.f32
 #include "attn_api.h"
 #include "attn_common.cuh"
 #include "common/host_util.h"
@@ -26,14 +25,14 @@
 namespace ra {
 namespace attn {
 
-constexpr int BWD_THREADS = 448;
+constexpr int BWD_THREADS = 512;
 
 struct BwdParams {
   int B, H;
   MaskParams mask;
   float scale;       // 1/sqrt(D)
   float scale_log2;  // log2(e)/sqrt(D)
-  const float* lse2;   // (B, H, Sq_pad): lse*log2(e), +inf for fully masked / padded rows
+  const float* lse2;   // (B, H, Sq_pad): -lse*log2(e), -inf for fully masked / padded rows
   const float* delta;  // (B, H, Sq_pad): rowsum(dO * O)
   int Sq_pad;
   float* dq_acc;       // (B, Sq, H, D) fp32 contiguous, accumulated with reductions
@@ -45,7 +44,6 @@ struct BwdParams {
   long long copy_n16;
   int copy_ctas;
   int* status;
-  int debug;
 };
 
 template <int D>
@@ -119,7 +117,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint8_t* sQ = smem + SM::Q_OFF;
   uint8_t* sDO = smem + SM::DO_OFF;
   uint8_t* sDS = smem + SM::DS_OFF;
-  float* sLse = reinterpret_cast<float*>(smem + SM::LSE_OFF);  // [stage][256]
+  float* sLse = reinterpret_cast<float*>(smem + SM::LSE_OFF);  // [stage][-lse2 128 | delta 128]
   int* sSegQ = reinterpret_cast<int*>(smem + SM::SEG_OFF);     // [buf][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* kv_full = bars;        // 1
@@ -186,9 +184,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const uint32_t tDV = tmem_base + 256;
   const uint32_t tDK = tmem_base + 384;
 
-  if (warp == 0) {
-    // ================================================================ TMA producer
-    if (lane == 0) {
+  if (warp < 4) {
+    // ================================================================ producer warpgroup
+    setmaxnreg_dec<48>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
       mbar_arrive_expect_tx(kv_full, 2 * SM::TILE_BYTES);
 #pragma unroll
       for (int s = 0; s < NSLAB; ++s) {
@@ -216,23 +216,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tma_load_4d(sDO + s * SM::SLAB_BYTES, &tma_do, do_full, s * 64, h, qi0, b);
         ++it;
       }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ================================================================ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, 0, 1);
       constexpr uint32_t idesc_dk = make_idesc_bf16(128, D, 0, 1);
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV), doa = smem_u32(sDO), dsa = smem_u32(sDS);
+      constexpr uint32_t SLAB = SM::SLAB_BYTES;
+      // descriptor bases: *_k = K-major view (rows of 128 B along the reduction dim),
+      // *_mn = MN-major view of the same bytes (64-wide slabs SLAB bytes apart)
+      const uint64_t k_k = make_smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t k_mn = make_smem_desc(smem_u32(sK), SLAB, 1024);
+      const uint64_t v_k = make_smem_desc(smem_u32(sV), 16, 1024);
+      const uint64_t do_k = make_smem_desc(smem_u32(sDO), 16, 1024);
+      const uint64_t do_mn = make_smem_desc(smem_u32(sDO), SLAB, 1024);
+      const uint64_t ds_k = make_smem_desc(smem_u32(sDS), 16, 1024);
+      const uint64_t ds_mn = make_smem_desc(smem_u32(sDS), SLAB, 1024);
+      const uint64_t q_k[2] = {make_smem_desc(smem_u32(sQ), 16, 1024),
+                               make_smem_desc(smem_u32(sQ + SM::TILE_BYTES), 16, 1024)};
+      const uint64_t q_mn[2] = {make_smem_desc(smem_u32(sQ), SLAB, 1024),
+                                make_smem_desc(smem_u32(sQ + SM::TILE_BYTES), SLAB, 1024)};
       auto issue_st = [&](int st) {  // S^T = K Q^T
-        const uint32_t qa = smem_u32(sQ + st * SM::TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SM::SLAB_BYTES + (kk & 3) * 32;
-          umma_ss(tS, make_smem_desc(ka + off, 16, 1024), make_smem_desc(qa + off, 16, 1024), idesc_s,
-                  kk != 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
+          umma_ss(tS, desc_advance(k_k, off), desc_advance(q_k[st], off), idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(s_full);
       };
@@ -254,16 +262,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       while (ok && i < nqt) {
         const int st = it & 1;
         const uint32_t par = it & 1;
-        const uint32_t qa = smem_u32(sQ + st * SM::TILE_BYTES);
-        // dP^T = V dO^T (the dP region doubles as dQ: wait until the previous dQ was drained)
+        // dP^T = V dO^T (its region doubles as dQ: wait until the previous dQ left TMEM)
         if (!mbar_wait(do_full, par, wc, kTimeoutSmemFull)) break;
         if (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, wc, kTimeoutTmemEmpty)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SM::SLAB_BYTES + (kk & 3) * 32;
-          umma_ss(tDP, make_smem_desc(va + off, 16, 1024), make_smem_desc(doa + off, 16, 1024),
-                  idesc_s, kk != 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
+          umma_ss(tDP, desc_advance(v_k, off), desc_advance(do_k, off), idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(dp_full);
         // dV += P^T dO
@@ -272,28 +278,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_col = tS + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-          umma_ts(tDV, a_col, make_smem_desc(doa + kk * 2048, SM::SLAB_BYTES, 1024), idesc_dv,
-                  (it != 0 || kk != 0) ? 1u : 0u);
+          umma_ts(tDV, a_col, desc_advance(do_mn, kk * 2048), idesc_dv, (it != 0 || kk != 0) ? 1u : 0u);
         }
         umma_commit(do_empty);
-        // dK += dS^T Q ; dQ_i = dS K
-        if (!mbar_wait(ds_ready, par, wc, kTimeoutTmemFull)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_off = (kk >> 2) * SM::SLAB_BYTES + (kk & 3) * 32;
-          umma_ss(tDK, make_smem_desc(dsa + a_off, 16, 1024),
-                  make_smem_desc(qa + kk * 2048, SM::SLAB_BYTES, 1024), idesc_dk,
-                  (it != 0 || kk != 0) ? 1u : 0u);
-        }
-        umma_commit(&q_empty[st]);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          umma_ss(tDP, make_smem_desc(dsa + kk * 2048, SM::SLAB_BYTES, 1024),
-                  make_smem_desc(ka + kk * 2048, SM::SLAB_BYTES, 1024), idesc_dq, kk != 0 ? 1u : 0u);
-        }
-        umma_commit(dq_full);
-        // next S^T as soon as its Q tile has landed (P^T was consumed by the dV MMAs above)
+        // next S^T right away (P^T was consumed by the dV MMAs just issued), so that the softmax
+        // group can work on it while dK/dQ of this iteration run
         const int in = next_visible(i + 1);
         if (in < nqt) {
           const int stn = (it + 1) & 1;
@@ -301,17 +290,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tc_fence_after();
           issue_st(stn);
         }
+        // dK += dS^T Q ; dQ_i = dS K
+        if (!mbar_wait(ds_ready, par, wc, kTimeoutTmemFull)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;
+          umma_ss(tDK, desc_advance(ds_k, a_off), desc_advance(q_mn[st], kk * 2048), idesc_dk,
+                  (it != 0 || kk != 0) ? 1u : 0u);
+        }
+        umma_commit(&q_empty[st]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tDP, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), idesc_dq,
+                  kk != 0 ? 1u : 0u);
+        umma_commit(dq_full);
         i = in;
         ++it;
       }
       umma_commit(acc_full);
     }
     __syncwarp();
-  } else if (warp < 10) {
+  } else if (warp < 12) {
     // ================================================================ softmax / dS group
+    setmaxnreg_inc<152>();
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 q-columns
-    const int sm_tid = (warp - 2) * 32 + lane;
+    const int half = (warp - 4) >> 2;  // which 64 q-columns
+    const int sm_tid = (warp - 4) * 32 + lane;
     const int row = quad * 32 + lane;  // kv row inside the tile
     const int kj = k0 + row;
     const bool row_valid = kj < mk.Sk;
@@ -323,6 +328,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const unsigned int bh_u = static_cast<unsigned int>(b * p.H + h);
     uint8_t* ds_row = sDS + half * SM::SLAB_BYTES + row * 128;
     const int swz = row & 7;
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    const uint64_t bias2 = f2_pack(my_bias2, my_bias2);
 
     int it = 0;
     bool alive = true;
@@ -339,8 +346,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         named_bar_sync(1, 256);
       }
       if (!mbar_wait(&q_full[st], (it >> 1) & 1, wc, kTimeoutSmemFull)) { alive = false; break; }
-      const float* lse2 = sLse + st * 256;
-      const float* dlt = lse2 + 128;
+      const float4* nl4 = reinterpret_cast<const float4*>(sLse + st * 256 + half * 64);
+      const float4* dl4 = reinterpret_cast<const float4*>(sLse + st * 256 + 128 + half * 64);
       if (!mbar_wait(s_full, par, wc, kTimeoutTmemFull)) { alive = false; break; }
       tc_fence_after();
 
@@ -356,30 +363,49 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       const unsigned int qpos0 = static_cast<unsigned int>(mk.qmap(qi0));
-      float pv[64];
+      uint64_t pv[32];  // 64 probabilities of this thread's row, as fp32 pairs
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t s[32];
         tmem_ld_x32(tS + lane_base + half * 64 + c * 32, s);
         tmem_ld_wait();
+        uint64_t x[16];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 n = nl4[c * 8 + g];
+          x[2 * g] = f2_fma(f2_pack_u(s[4 * g], s[4 * g + 1]), scale2, f2_pack(n.x, n.y));
+          x[2 * g + 1] = f2_fma(f2_pack_u(s[4 * g + 2], s[4 * g + 3]), scale2, f2_pack(n.z, n.w));
+        }
+        if (!plain) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            x[e] = f2_add(x[e], bias2);
+            float x0, x1;
+            f2_unpack(x[e], x0, x1);
+            const int col = half * 64 + c * 32 + 2 * e;
+            bool m0 = col < lo, m1 = (col + 1) < lo;
+            if (mk.seg_q) {
+              m0 |= (sSegQ[st * 128 + col] != my_seg);
+              m1 |= (sSegQ[st * 128 + col + 1] != my_seg);
+            }
+            if (mk.drop_threshold) {
+              m0 |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + col,
+                                 static_cast<unsigned int>(kpos)) < mk.drop_threshold;
+              m1 |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + col + 1,
+                                 static_cast<unsigned int>(kpos)) < mk.drop_threshold;
+            }
+            x[e] = f2_pack(m0 ? -INFINITY : x0, m1 ? -INFINITY : x1);
+          }
+        }
         uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = half * 64 + c * 32 + e;
-          float x = fmaf(__uint_as_float(s[e]), p.scale_log2, my_bias2) - lse2[col];
-          float pr = (p.debug & 4) ? x : exp2_approx(x);
-          if (!plain) {
-            bool masked = col < lo;
-            if (mk.seg_q) masked |= (sSegQ[st * 128 + col] != my_seg);
-            if (mk.drop_threshold)
-              masked |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + col,
-                                     static_cast<unsigned int>(kpos)) < mk.drop_threshold;
-            pr = masked ? 0.f : pr;
-          }
-          pv[c * 32 + e] = pr;
+        for (int e = 0; e < 16; ++e) {
+          float x0, x1;
+          f2_unpack(x[e], x0, x1);
+          const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+          pv[c * 16 + e] = f2_pack(p0, p1);
+          pk[e] = pack_bf16x2(p0, p1);
         }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pk[e] = pack_bf16x2(pv[c * 32 + 2 * e], pv[c * 32 + 2 * e + 1]);
         tmem_st_x16(tS + lane_base + half * 64 + c * 16, pk);
       }
       tmem_st_wait();
@@ -397,17 +423,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          float ds[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int cc = c * 32 + g * 8 + e;
-            ds[e] = pv[cc] * (__uint_as_float(dp[g * 8 + e]) - dlt[half * 64 + cc]) * p.scale;
-          }
+          const float4 d0 = dl4[c * 8 + 2 * g], d1 = dl4[c * 8 + 2 * g + 1];
+          const uint64_t t0 = f2_mul(pv[c * 16 + 4 * g], f2_sub(f2_pack_u(dp[8 * g], dp[8 * g + 1]), f2_pack(d0.x, d0.y)));
+          const uint64_t t1 = f2_mul(pv[c * 16 + 4 * g + 1], f2_sub(f2_pack_u(dp[8 * g + 2], dp[8 * g + 3]), f2_pack(d0.z, d0.w)));
+          const uint64_t t2 = f2_mul(pv[c * 16 + 4 * g + 2], f2_sub(f2_pack_u(dp[8 * g + 4], dp[8 * g + 5]), f2_pack(d1.x, d1.y)));
+          const uint64_t t3 = f2_mul(pv[c * 16 + 4 * g + 3], f2_sub(f2_pack_u(dp[8 * g + 6], dp[8 * g + 7]), f2_pack(d1.z, d1.w)));
+          float a0, a1, a2, a3, a4, a5, a6, a7;
+          f2_unpack(t0, a0, a1);
+          f2_unpack(t1, a2, a3);
+          f2_unpack(t2, a4, a5);
+          f2_unpack(t3, a6, a7);
           uint4 v;
-          v.x = pack_bf16x2(ds[0], ds[1]);
-          v.y = pack_bf16x2(ds[2], ds[3]);
-          v.z = pack_bf16x2(ds[4], ds[5]);
-          v.w = pack_bf16x2(ds[6], ds[7]);
+          v.x = pack_bf16x2(a0, a1);
+          v.y = pack_bf16x2(a2, a3);
+          v.z = pack_bf16x2(a4, a5);
+          v.w = pack_bf16x2(a6, a7);
           const int chunk = c * 4 + g;  // 16-byte chunk inside the 128-byte row
           *reinterpret_cast<uint4*>(ds_row + ((chunk ^ swz) << 4)) = v;
         }
@@ -418,13 +448,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       ++it;
     }
 
-    // ---- epilogue: dV (half 0) / dK (half 1) for this warp's 32 kv rows
+    // ---- epilogue: dV (half 0) / dK (half 1) for this warp's 32 kv rows. dS carried no softmax
+    // scale, so dK is scaled here.
     if (alive) alive = mbar_wait(acc_full, 0, wc, kTimeoutTmemFull);
     alive = __all_sync(0xffffffffu, alive);  // TMEM loads below are warp-collective
     tc_fence_after();
     if (alive && !(it == 0 && p.dkv_mode == 2)) {
       const uint32_t tacc = (half == 0 ? tDV : tDK) + lane_base;
       void* base = half == 0 ? p.dv : p.dk;
+      const float mul = half == 0 ? 1.0f : p.scale;
       const long long off = b * p.dkv_sb + static_cast<long long>(kj) * p.dkv_ss + h * p.dkv_sh;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
@@ -437,33 +469,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           for (int e = 0; e < 32; ++e) r[e] = 0u;
         }
         if (!row_valid) continue;
+        float f[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(r[e]) * mul;
         if (p.dkv_mode == 0) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + off + c * 32;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
+            v.x = pack_bf16x2(f[8 * g], f[8 * g + 1]);
+            v.y = pack_bf16x2(f[8 * g + 2], f[8 * g + 3]);
+            v.z = pack_bf16x2(f[8 * g + 4], f[8 * g + 5]);
+            v.w = pack_bf16x2(f[8 * g + 6], f[8 * g + 7]);
             *reinterpret_cast<uint4*>(dst + 8 * g) = v;
           }
         } else {
           float* dst = reinterpret_cast<float*>(base) + off + c * 32;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
-            const float a0 = __uint_as_float(r[4 * g]), a1 = __uint_as_float(r[4 * g + 1]);
-            const float a2 = __uint_as_float(r[4 * g + 2]), a3 = __uint_as_float(r[4 * g + 3]);
             if (p.dkv_mode == 1)
-              *reinterpret_cast<float4*>(dst + 4 * g) = make_float4(a0, a1, a2, a3);
+              *reinterpret_cast<float4*>(dst + 4 * g) =
+                  make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
             else
-              red_add_v4_sys(dst + 4 * g, a0, a1, a2, a3);
+              red_add_v4_sys(dst + 4 * g, f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
           }
         }
       }
     }
   } else {
     // ================================================================ dQ drain group
+    setmaxnreg_inc<160>();
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // q row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -471,24 +506,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     for (int i = 0; i < nqt; ++i) {
       const int qi0 = i * 128;
       if (!tile_visible(mk, b, qi0, k0)) continue;
-      if (!mbar_wait(dq_full, it & 1, wc, kTimeoutTmemFull)) break;
+      bool ok = mbar_wait(dq_full, it & 1, wc, kTimeoutTmemFull);
+      if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();
       const int qi = qi0 + row;
       float* dst = p.dq_acc + ((static_cast<long long>(b) * mk.Sq + qi) * p.H + h) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(tDP + lane_base + c * 32, r);
-        tmem_ld_wait();
-        if (qi < mk.Sq && !(p.debug & 1)) {
+      // pull the whole dQ tile into registers, hand the TMEM region back, then reduce
+      uint32_t r[D];
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            red_add_v4(dst + c * 32 + 4 * g, __uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                       __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-        }
-      }
+      for (int c = 0; c < D / 32; ++c) tmem_ld_x32(tDP + lane_base + c * 32, r + c * 32);
+      tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_empty);
+      if (qi < mk.Sq) {
+#pragma unroll
+        for (int g = 0; g < D / 4; ++g)
+          red_add_v4(dst + 4 * g, __uint_as_float(r[4 * g]) * p.scale, __uint_as_float(r[4 * g + 1]) * p.scale,
+                     __uint_as_float(r[4 * g + 2]) * p.scale, __uint_as_float(r[4 * g + 3]) * p.scale);
+      }
       ++it;
     }
   }
@@ -503,8 +538,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   }
 }
 
-// delta[b,h,q] = sum_d dO*O ; lse2 = lse*log2(e) (+inf where lse is -inf); padded rows get
-// (+inf, 0) so that they contribute nothing. One warp per (b, q, h) row.
+// delta[b,h,q] = sum_d dO*O ; lse2 = -lse*log2(e) (-inf where lse is -inf); padded rows get
+// (-inf, 0) so that exp2(s*c + lse2) is 0 for them. One warp per (b, q, h) row.
 template <int D>
 __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_ss,
                                      long long o_sh, const __nv_bfloat16* __restrict__ d_o,
@@ -519,7 +554,7 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, long l
   const int hh = static_cast<int>((gw / Sq_pad) % H);
   const int bb = static_cast<int>(gw / (static_cast<long long>(Sq_pad) * H));
   float acc = 0.f;
-  float l2 = INFINITY;
+  float l2 = -INFINITY;
   if (q < Sq) {
     const __nv_bfloat16* po = o + bb * o_sb + static_cast<long long>(q) * o_ss + hh * o_sh;
     const __nv_bfloat16* pd = d_o + bb * do_sb + static_cast<long long>(q) * do_ss + hh * do_sh;
@@ -534,7 +569,7 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, long l
 #pragma unroll
     for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
     const float l = lse[(static_cast<long long>(bb) * H + hh) * Sq + q];
-    l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+    l2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
   }
   if (lane == 0) {
     lse2[gw] = l2;
@@ -613,7 +648,6 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   p.copy_n16 = a->copy_bytes / 16;
   p.copy_ctas = (a->copy_src && a->copy_bytes > 0) ? a->copy_ctas : 0;
   p.status = a->status;
-  { const char* e = getenv("RINGATTN_B200_BWD_DEBUG"); p.debug = e ? atoi(e) : 0; }
   const int nkt = (a->Sk + 127) / 128;
   const long long grid = static_cast<long long>(nkt) * a->H * a->B + p.copy_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);

@@ -2,10 +2,10 @@
 //
 // One CTA owns 256 query rows (two 128-row tiles) of one (batch, head) and walks the visible
 // 128-row KV tiles:
-//   warp 0      TMA producer (Q once, K/V through a 2-stage ring each)
-//   warp 1      tcgen05.mma issuer: S_w = Q_w K^T (SS) and O_w += P_w V (P read from TMEM)
-//   warps 2-5   softmax group for tile 0, warps 6-9 for tile 1: tcgen05.ld S, mask, online
-//               softmax with lazy rescale of O in TMEM, P written back over S as packed bf16
+//   warps 0-3   producer group (registers trimmed): warp 0 TMA (Q once, K/V through a 2-stage
+//               ring each), warp 1 tcgen05.mma issuer: S_w = Q_w K^T (SS), O_w += P_w V (P in TMEM)
+//   warps 4-7   softmax group for tile 0, warps 8-11 for tile 1 (registers raised): tcgen05.ld S,
+//               mask, online softmax with lazy rescale of O in TMEM, P written back over S as bf16
 // TMEM: S0 | S1 | O0 | O1 (4 x 128 columns). While one group runs its softmax the tensor core
 // works on the other tile, so MMA and exp overlap without a third party.
 //
@@ -19,7 +19,7 @@
 namespace ra {
 namespace attn {
 
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 384;
 constexpr int KV_STAGES = 2;
 
 struct FwdParams {
@@ -148,6 +148,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const uint32_t tS[2] = {tmem_base, tmem_base + 128};
   const uint32_t tO[2] = {tmem_base + 256, tmem_base + 384};
 
+  if (warp < 4) setmaxnreg_dec<48>();
   if (warp == 0) {
     // ================================================================ TMA producer
     if (lane == 0) {
@@ -185,24 +186,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+      const uint64_t q_desc[2] = {make_smem_desc(smem_u32(sQ), 16, 1024),
+                                  make_smem_desc(smem_u32(sQ + SM::Q_TILE_BYTES), 16, 1024)};
+      const uint64_t k_desc[2] = {make_smem_desc(smem_u32(sK), 16, 1024),
+                                  make_smem_desc(smem_u32(sK + SM::KV_TILE_BYTES), 16, 1024)};
+      const uint64_t v_desc[2] = {make_smem_desc(smem_u32(sV), SM::SLAB_BYTES, 1024),
+                                  make_smem_desc(smem_u32(sV + SM::KV_TILE_BYTES), SM::SLAB_BYTES, 1024)};
       auto issue_s = [&](int w, int st) {
-        const uint32_t qa = smem_u32(sQ + w * SM::Q_TILE_BYTES);
-        const uint32_t ka = smem_u32(sK + st * SM::KV_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SM::SLAB_BYTES + (kk & 3) * 32;
-          umma_ss(tS[w], make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
-                  idesc_s, kk != 0 ? 1u : 0u);
+          umma_ss(tS[w], desc_advance(q_desc[w], off), desc_advance(k_desc[st], off), idesc_s,
+                  kk != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[w]);
       };
       auto issue_pv = [&](int w, int st, bool acc) {
-        const uint32_t va = smem_u32(sV + st * SM::KV_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // A = P_w in TMEM: 16 bf16 of K per step = 8 columns. B = V, MN-major: 16 kv rows = 2 KiB.
-          umma_ts(tO[w], tS[w] + kk * 8, make_smem_desc(va + kk * 2048, SM::SLAB_BYTES, 1024),
-                  idesc_o, (acc || kk != 0) ? 1u : 0u);
+          umma_ts(tO[w], tS[w] + kk * 8, desc_advance(v_desc[st], kk * 2048), idesc_o,
+                  (acc || kk != 0) ? 1u : 0u);
         }
         umma_commit(&o_done[w]);
       };
@@ -272,12 +276,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp >= 4) {
     // ================================================================ softmax groups
-    const int w = (warp - 2) >> 2;  // q tile handled by this group
+    setmaxnreg_inc<216>();
+    const int w = (warp - 4) >> 2;  // q tile handled by this group
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int wg_tid = ((warp - 2) & 3) * 32 + lane;
+    const int wg_tid = quad * 32 + lane;
     const int qi0 = q0 + w * 128;
     const int qi = qi0 + row;
     const bool row_valid = qi < mk.Sq;
@@ -320,8 +325,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       float sc = p.scale_log2;  // multiplier still to be applied to sr[] inside the exp
       float mx = -INFINITY;
       if (plain) {
+        mx = fmaxf(__uint_as_float(sr[0]), __uint_as_float(sr[1]));
 #pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+        for (int i = 2; i < 128; i += 2) mx = max3(mx, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
         mx *= sc;
       } else {
         const int limit = causal_col_limit(mk, qpos, k0);
@@ -372,16 +378,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      const float neg_m = -m_use;
-      float sum = 0.f;
+      const uint64_t neg_m2 = f2_pack(-m_use, -m_use);
+      const uint64_t sc2 = f2_pack(sc, sc);
+      uint64_t sum2 = f2_pack(0.f, 0.f);
       uint32_t pk[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        const float p0 = exp2_approx(fmaf(__uint_as_float(sr[2 * i]), sc, neg_m));
-        const float p1 = exp2_approx(fmaf(__uint_as_float(sr[2 * i + 1]), sc, neg_m));
-        sum += p0 + p1;
+        float x0, x1;
+        f2_unpack(f2_fma(f2_pack_u(sr[2 * i], sr[2 * i + 1]), sc2, neg_m2), x0, x1);
+        const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+        sum2 = f2_add(sum2, f2_pack(p0, p1));
         pk[i] = pack_bf16x2(p0, p1);
       }
+      float sum, sum_hi;
+      f2_unpack(sum2, sum, sum_hi);
+      sum += sum_hi;
       l += sum;
       tmem_st_x32(tS[w] + lane_base, pk);
       tmem_st_x32(tS[w] + lane_base + 32, pk + 32);
