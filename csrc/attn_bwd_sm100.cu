@@ -10,14 +10,14 @@
 //     dV  += P^T dO_i           (A from TMEM)        -> TMEM [256,256+D)
 //     dK  += dS^T Q_i           (A = dS^T, K-major)  -> TMEM [384,384+D)
 //     dQ_i = dS K               (A = dS^T read MN-major, B = K MN-major) -> TMEM over dP^T
-// dQ_i is added to an fp32 buffer with vector reductions; dK/dV leave through the epilogue as
+// dQ_i is added to an fp32 buffer with bulk tensor reductions (TMA, staged through shared memory); dK/dV leave through the epilogue as
 // bf16, fp32 or as fp32 reductions into (possibly a peer GPU's) accumulators, which is how the
 // ring backward returns gradients to the owner of the KV block.
 //
 //   warps 0-3    producer group (registers trimmed): warp 0 TMA (K,V once; Q_i + lse/delta
 //                double-buffered; dO_i), warp 1 tcgen05.mma issuer
 //   warps 4-11   softmax/dS group: two warps per TMEM lane quadrant, 64 q-columns each
-//   warps 12-15  dQ drain group (registers raised): tcgen05.ld, early release, red.global.add.v4.f32
+//   warps 12-15  dQ drain group (registers raised): tcgen05.ld, early release, bulk reduce-add
 #include "attn_api.h"
 #include "attn_common.cuh"
 #include "common/host_util.h"
@@ -44,6 +44,7 @@ struct BwdParams {
   long long copy_n16;
   int copy_ctas;
   int* status;
+  long long* trace;  // optional phase timestamps of the first compute CTA: [role 0..2][64 iterations][4]
 };
 
 template <int D>
@@ -55,7 +56,8 @@ struct BwdSmem {
   static constexpr int Q_OFF = V_OFF + TILE_BYTES;        // 2 stages
   static constexpr int DO_OFF = Q_OFF + 2 * TILE_BYTES;   // 1 stage
   static constexpr int DS_OFF = DO_OFF + TILE_BYTES;      // 128 x 128 bf16
-  static constexpr int LSE_OFF = DS_OFF + 128 * 128 * 2;  // [2 stages][lse2 128 | delta 128]
+  static constexpr int DQ_OFF = DS_OFF + 128 * 128 * 2;   // dQ staging: 128 rows x 32 fp32, swizzled
+  static constexpr int LSE_OFF = DQ_OFF + 128 * 32 * 4;   // [2 stages][lse2 128 | delta 128]
   static constexpr int SEG_OFF = LSE_OFF + 2 * 256 * 4;   // [2][128] int
   static constexpr int BAR_OFF = SEG_OFF + 2 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
@@ -80,11 +82,17 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
                : "memory");
 }
 
+// Phase timestamps (SM clock) for pipeline analysis; only the first compute CTA records, only its
+// first 64 iterations, and only when a trace buffer was registered with ra_set_bwd_trace().
+__device__ __forceinline__ void trace_event(long long* trace, bool on, int role, int it, int slot) {
+  if (on && it < 64) trace[(role * 64 + it) * 4 + slot] = clock64();
+}
+
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                 const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_do,
-                const BwdParams p) {
+                const __grid_constant__ CUtensorMap tma_dq, const BwdParams p) {
   using SM = BwdSmem<D>;
   constexpr int NSLAB = D / 64;
 
@@ -117,6 +125,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint8_t* sQ = smem + SM::Q_OFF;
   uint8_t* sDO = smem + SM::DO_OFF;
   uint8_t* sDS = smem + SM::DS_OFF;
+  uint8_t* sDQ = smem + SM::DQ_OFF;
   float* sLse = reinterpret_cast<float*>(smem + SM::LSE_OFF);  // [stage][-lse2 128 | delta 128]
   int* sSegQ = reinterpret_cast<int*>(smem + SM::SEG_OFF);     // [buf][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
@@ -148,6 +157,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const int h = bh % p.H;
   const int b = bh / p.H;
   const int k0 = jt * 128;
+  const bool tr = p.trace != nullptr && idx == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -170,6 +180,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     tma_prefetch_desc(&tma_k);
     tma_prefetch_desc(&tma_v);
     tma_prefetch_desc(&tma_do);
+    tma_prefetch_desc(&tma_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -266,6 +277,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (!mbar_wait(do_full, par, wc, kTimeoutSmemFull)) break;
         if (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, wc, kTimeoutTmemEmpty)) break;
         tc_fence_after();
+        trace_event(p.trace, tr, 0, it, 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
@@ -275,6 +287,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         // dV += P^T dO
         if (!mbar_wait(p_ready, par, wc, kTimeoutTmemFull)) break;
         tc_fence_after();
+        trace_event(p.trace, tr, 0, it, 1);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_col = tS + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
@@ -293,6 +306,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         // dK += dS^T Q ; dQ_i = dS K
         if (!mbar_wait(ds_ready, par, wc, kTimeoutTmemFull)) break;
         tc_fence_after();
+        trace_event(p.trace, tr, 0, it, 2);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;
@@ -305,6 +319,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           umma_ss(tDP, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), idesc_dq,
                   kk != 0 ? 1u : 0u);
         umma_commit(dq_full);
+        trace_event(p.trace, tr, 0, it, 3);
         i = in;
         ++it;
       }
@@ -350,6 +365,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const float4* dl4 = reinterpret_cast<const float4*>(sLse + st * 256 + 128 + half * 64);
       if (!mbar_wait(s_full, par, wc, kTimeoutTmemFull)) { alive = false; break; }
       tc_fence_after();
+      trace_event(p.trace, tr && sm_tid == 0, 1, it, 0);
 
       // masked iff column (q index) c < lo: causal rule transposed; everything if the row is padding
       int lo = 0;
@@ -411,11 +427,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_ready);
+      trace_event(p.trace, tr && sm_tid == 0, 1, it, 1);
 
       if (!mbar_wait(dp_full, par, wc, kTimeoutTmemFull)) { alive = false; break; }
       // the dS buffer is still being read by the previous dK/dQ MMAs until dq_full fires
       if (it > 0 && !mbar_wait(dq_full, (it - 1) & 1, wc, kTimeoutTmemFull)) { alive = false; break; }
       tc_fence_after();
+      trace_event(p.trace, tr && sm_tid == 0, 1, it, 2);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t dp[32];
@@ -445,6 +463,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(ds_ready);
+      trace_event(p.trace, tr && sm_tid == 0, 1, it, 3);
       ++it;
     }
 
@@ -509,23 +528,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       bool ok = mbar_wait(dq_full, it & 1, wc, kTimeoutTmemFull);
       if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();
-      const int qi = qi0 + row;
-      float* dst = p.dq_acc + ((static_cast<long long>(b) * mk.Sq + qi) * p.H + h) * D;
-      // pull the whole dQ tile into registers, hand the TMEM region back, then reduce
+      trace_event(p.trace, tr && warp == 12 && lane == 0, 2, it, 0);
+      // pull the whole dQ tile into registers and hand the TMEM region back at once; then move it
+      // to global memory with bulk tensor reductions staged through one 16 KiB shared buffer
       uint32_t r[D];
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) tmem_ld_x32(tDP + lane_base + c * 32, r + c * 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_empty);
-      if (qi < mk.Sq) {
+      trace_event(p.trace, tr && warp == 12 && lane == 0, 2, it, 1);
+      uint8_t* dq_row = sDQ + row * 128;
+      const int swz = row & 7;
 #pragma unroll
-        for (int g = 0; g < D / 4; ++g)
-          red_add_v4(dst + 4 * g, __uint_as_float(r[4 * g]) * p.scale, __uint_as_float(r[4 * g + 1]) * p.scale,
-                     __uint_as_float(r[4 * g + 2]) * p.scale, __uint_as_float(r[4 * g + 3]) * p.scale);
+      for (int c = 0; c < D / 32; ++c) {
+        if (warp == 12 && lane == 0) tma_store_wait_read<0>();  // staging buffer free again
+        named_bar_sync(2, 128);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 v = make_float4(__uint_as_float(r[c * 32 + 4 * g]) * p.scale,
+                                       __uint_as_float(r[c * 32 + 4 * g + 1]) * p.scale,
+                                       __uint_as_float(r[c * 32 + 4 * g + 2]) * p.scale,
+                                       __uint_as_float(r[c * 32 + 4 * g + 3]) * p.scale);
+          *reinterpret_cast<float4*>(dq_row + ((g ^ swz) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(2, 128);
+        if (warp == 12 && lane == 0) {
+          tma_reduce_add_4d(&tma_dq, sDQ, c * 32, h, qi0, b);
+          tma_store_commit();
+        }
       }
+      trace_event(p.trace, tr && warp == 12 && lane == 0, 2, it, 2);
       ++it;
     }
+    if (warp == 12 && lane == 0) tma_store_wait_all<0>();  // reductions complete before the CTA retires
   }
 
   // ------------------------------------------------------------------ teardown
@@ -593,6 +630,16 @@ int make_bshd_map_bwd(CUtensorMap* m, const void* base, int B, int S, int H, int
 }  // namespace
 
 
+namespace {
+long long* g_bwd_trace = nullptr;
+}
+// Register (or clear, with nullptr) a device buffer of 3*64*4 int64 that the first compute CTA of
+// every later backward launch fills with SM-clock timestamps of its pipeline phases.
+extern "C" int ra_set_bwd_trace(long long* buf) {
+  g_bwd_trace = buf;
+  return 0;
+}
+
 extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   using namespace ra;
   using namespace ra::attn;
@@ -613,6 +660,19 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   if ((rc = make_bshd_map_bwd(&tv, a->v, a->B, a->Sk, a->H, a->D, a->v_sb, a->v_ss, a->v_sh))) return rc;
   if ((rc = make_bshd_map_bwd(&tdo, a->d_o, a->B, a->Sq, a->H, a->D, a->do_sb, a->do_ss, a->do_sh)))
     return rc;
+  CUtensorMap tdq;
+  {
+    if (reinterpret_cast<uintptr_t>(a->dq_acc) & 15) {
+      set_error("ra_attn_bwd: dq_acc must be 16-byte aligned");
+      return kHostBadArg;
+    }
+    uint64_t dims[4] = {static_cast<uint64_t>(a->D), static_cast<uint64_t>(a->H),
+                        static_cast<uint64_t>(a->Sq), static_cast<uint64_t>(a->B)};
+    uint64_t str[3] = {static_cast<uint64_t>(a->D) * 4, static_cast<uint64_t>(a->H) * a->D * 4,
+                       static_cast<uint64_t>(a->Sq) * a->H * a->D * 4};
+    uint32_t box[4] = {32, 1, 128, 1};
+    if ((rc = make_tmap_f32_sw128(&tdq, a->dq_acc, 4, dims, str, box))) return rc;
+  }
   BwdParams p;
   p.B = a->B;
   p.H = a->H;
@@ -648,6 +708,7 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   p.copy_n16 = a->copy_bytes / 16;
   p.copy_ctas = (a->copy_src && a->copy_bytes > 0) ? a->copy_ctas : 0;
   p.status = a->status;
+  p.trace = g_bwd_trace;
   const int nkt = (a->Sk + 127) / 128;
   const long long grid = static_cast<long long>(nkt) * a->H * a->B + p.copy_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);
@@ -658,7 +719,7 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
       set_error("attn_bwd: smem attribute");
       return kHostLaunchFail;
     }
-    kern<<<static_cast<unsigned>(grid), BWD_THREADS, BwdSmem<128>::TOTAL, s>>>(tq, tk, tv, tdo, p);
+    kern<<<static_cast<unsigned>(grid), BWD_THREADS, BwdSmem<128>::TOTAL, s>>>(tq, tk, tv, tdo, tdq, p);
   } else {
     auto kern = attn_bwd_kernel<64>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::TOTAL) !=
@@ -666,7 +727,7 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
       set_error("attn_bwd: smem attribute");
       return kHostLaunchFail;
     }
-    kern<<<static_cast<unsigned>(grid), BWD_THREADS, BwdSmem<64>::TOTAL, s>>>(tq, tk, tv, tdo, p);
+    kern<<<static_cast<unsigned>(grid), BWD_THREADS, BwdSmem<64>::TOTAL, s>>>(tq, tk, tv, tdo, tdq, p);
   }
   return check_launch("attn_bwd_kernel");
 }
