@@ -44,7 +44,7 @@ struct BwdParams {
   long long copy_n16;
   int copy_ctas;
   int* status;
-  long long* trace;  // optional phase timestamps of the first compute CTA: [role 0..2][64 iterations][4]
+  long long* trace;  // optional phase timestamps of the first compute CTA: [role 0..3][64 iterations][4]
 };
 
 template <int D>
@@ -197,7 +197,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
   if (warp < 4) {
     // ================================================================ producer warpgroup
-    setmaxnreg_dec<48>();
+    setmaxnreg_dec<80>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       mbar_arrive_expect_tx(kv_full, 2 * SM::TILE_BYTES);
@@ -211,7 +211,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         const int qi0 = i * 128;
         if (!tile_visible(mk, b, qi0, k0)) continue;
         const int st = it & 1;
-        if (!mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1u, wc, kTimeoutSmemEmpty)) break;
+        if (!mbar_wait_relaxed(&q_empty[st], ((it >> 1) & 1) ^ 1u, wc, kTimeoutSmemEmpty)) break;
         mbar_arrive_expect_tx(&q_full[st], SM::TILE_BYTES + 1024);
 #pragma unroll
         for (int s = 0; s < NSLAB; ++s)
@@ -220,7 +220,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         const long long row_off = (static_cast<long long>(b) * p.H + h) * p.Sq_pad + qi0;
         bulk_load_1d(sLse + st * 256, p.lse2 + row_off, 512, &q_full[st]);
         bulk_load_1d(sLse + st * 256 + 128, p.delta + row_off, 512, &q_full[st]);
-        if (it > 0 && !mbar_wait(do_empty, (it - 1) & 1, wc, kTimeoutSmemEmpty)) break;
+        if (it > 0 && !mbar_wait_relaxed(do_empty, (it - 1) & 1, wc, kTimeoutSmemEmpty)) break;
         mbar_arrive_expect_tx(do_full, SM::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < NSLAB; ++s)
@@ -328,7 +328,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     __syncwarp();
   } else if (warp < 12) {
     // ================================================================ softmax / dS group
-    setmaxnreg_inc<152>();
+    setmaxnreg_inc<144>();
     const int quad = warp & 3;
     const int half = (warp - 4) >> 2;  // which 64 q-columns
     const int sm_tid = (warp - 4) * 32 + lane;
@@ -385,6 +385,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         uint32_t s[32];
         tmem_ld_x32(tS + lane_base + half * 64 + c * 32, s);
         tmem_ld_wait();
+        trace_event(p.trace, tr && sm_tid == 0, 3, it, c * 2);
         uint64_t x[16];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -423,6 +424,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           pk[e] = pack_bf16x2(p0, p1);
         }
         tmem_st_x16(tS + lane_base + half * 64 + c * 16, pk);
+        trace_event(p.trace, tr && sm_tid == 0, 3, it, c * 2 + 1);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -517,7 +519,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
   } else {
     // ================================================================ dQ drain group
-    setmaxnreg_inc<160>();
+    setmaxnreg_inc<144>();
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // q row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -525,7 +527,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     for (int i = 0; i < nqt; ++i) {
       const int qi0 = i * 128;
       if (!tile_visible(mk, b, qi0, k0)) continue;
-      bool ok = mbar_wait(dq_full, it & 1, wc, kTimeoutTmemFull);
+      bool ok = mbar_wait_relaxed(dq_full, it & 1, wc, kTimeoutTmemFull, 32);
       if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();
       trace_event(p.trace, tr && warp == 12 && lane == 0, 2, it, 0);

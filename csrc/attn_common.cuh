@@ -34,7 +34,9 @@ struct MaskParams {
 // segment-id ranges of the two tiles are disjoint. qi0/k0 are local start indices.
 __device__ __forceinline__ bool tile_visible(const MaskParams& m, int b, int qi0, int k0) {
   if (qi0 >= m.Sq || k0 >= m.Sk) return false;
-  if (m.cbs) {
+  if (m.cbs == 1) {  // plain causal: no divisions on the hot path
+    if (m.qmap(min(qi0 + 127, m.Sq - 1)) < m.kmap(k0)) return false;
+  } else if (m.cbs) {
     const int q_hi = m.qmap(min(qi0 + 127, m.Sq - 1));
     const int k_lo = m.kmap(k0);
     if (q_hi / m.cbs < k_lo / m.cbs) return false;
@@ -52,7 +54,9 @@ __device__ __forceinline__ bool tile_visible(const MaskParams& m, int b, int qi0
 __device__ __forceinline__ bool tile_plain(const MaskParams& m, int qi0, int k0) {
   if (m.seg_q || m.bias || m.drop_threshold) return false;
   if (k0 + 128 > m.Sk) return false;
-  if (m.cbs) {
+  if (m.cbs == 1) {
+    if (m.qmap(qi0) < m.kmap(min(k0 + 127, m.Sk - 1))) return false;
+  } else if (m.cbs) {
     const int q_lo = m.qmap(qi0);
     const int k_hi = m.kmap(min(k0 + 127, m.Sk - 1));
     if (q_lo / m.cbs < k_hi / m.cbs) return false;
@@ -66,7 +70,8 @@ __device__ __forceinline__ int causal_col_limit(const MaskParams& m, int qpos, i
   int limit = m.Sk - k0;
   if (m.cbs) {
     const int kbase = m.kmap(k0);
-    const long long lim = (static_cast<long long>(qpos / m.cbs) + 1) * m.cbs - kbase;
+    const long long lim =
+        (m.cbs == 1 ? static_cast<long long>(qpos) + 1 : (static_cast<long long>(qpos / m.cbs) + 1) * m.cbs) - kbase;
     limit = static_cast<int>(lim < limit ? (lim < 0 ? 0 : lim) : limit);
   }
   return limit;

@@ -148,7 +148,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const uint32_t tS[2] = {tmem_base, tmem_base + 128};
   const uint32_t tO[2] = {tmem_base + 256, tmem_base + 384};
 
-  if (warp < 4) setmaxnreg_dec<48>();
+  if (warp < 4) setmaxnreg_dec<72>();
   if (warp == 0) {
     // ================================================================ TMA producer
     if (lane == 0) {
@@ -165,13 +165,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (!(tile_visible(mk, b, q0, k0) || tile_visible(mk, b, q0 + 128, k0))) continue;
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1u, wc, kTimeoutSmemEmpty)) break;
+        if (!mbar_wait_relaxed(&k_empty[st], ph ^ 1u, wc, kTimeoutSmemEmpty)) break;
         mbar_arrive_expect_tx(&k_full[st], SM::KV_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < NSLAB; ++s)
           tma_load_4d(sK + st * SM::KV_TILE_BYTES + s * SM::SLAB_BYTES, &tma_k, &k_full[st], s * 64,
                       h, k0, b);
-        if (!mbar_wait(&v_empty[st], ph ^ 1u, wc, kTimeoutSmemEmpty)) break;
+        if (!mbar_wait_relaxed(&v_empty[st], ph ^ 1u, wc, kTimeoutSmemEmpty)) break;
         mbar_arrive_expect_tx(&v_full[st], SM::KV_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < NSLAB; ++s)

@@ -66,11 +66,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(0x989680u)  // let the hardware park the thread
       : "memory");
   return ok != 0;
 }
@@ -94,6 +94,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
   while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (((++it) & 63u) == 0u) {
+      if (*w.abort_smem) return false;
+      if (globaltimer_ns() - t0 > RA_WAIT_TIMEOUT_NS) {
+        raise_abort(w, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Same contract as mbar_wait for roles that are not latency critical (a producer waiting for a
+// free stage): sleeps between polls so that it does not compete with the working warps for issue
+// slots and shared-memory bandwidth.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                                  int code, unsigned sleep_ns = 64) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*w.abort_smem) return false;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if (((++it) & 63u) == 0u) {
       if (*w.abort_smem) return false;
