@@ -1,0 +1,392 @@
+// Decode attention over a sequence-sharded KV cache that stays where it is.
+//
+// The reference's inference op rotates the whole KV cache around the ring for every call
+// (ringattention/ringattention_inference.py:17-33). Here each GPU reads its own shard exactly once:
+//   1. decode_splitkv_kernel : the shard is cut into `splits` row ranges, one CTA per (range, head,
+//      batch). A few query rows (QL <= 8) are held in registers; K/V stream from HBM with 16-byte
+//      loads, several rows in flight per thread; online softmax in fp32; each CTA emits a partial
+//      (o, lse) for its range.
+//   2. decode_merge_kernel   : merges partials with log-sum-exp weights. In the ring variant the
+//      merged per-GPU result is *stored into every peer's inbox* (plain stores to peer memory), and
+//      after a flag barrier the same kernel merges the N per-GPU partials; every rank ends up with
+//      the identical result, as the reference's rotation would give.
+// The work is a batched GEMV: HBM bandwidth is the roofline, so it runs on the CUDA cores.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "common/host_util.h"
+
+namespace ra {
+namespace decode {
+
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
+
+struct SplitParams {
+  const __nv_bfloat16* q;  // (B, QL, H, D) contiguous
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  long long k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;  // element strides of the (B, S, H, D) cache views
+  float* o_part;    // (B, H, QL, splits, D) fp32, normalised partial outputs
+  float* lse_part;  // (B, H, QL, splits)
+  const uint8_t* mask;  // (B, Hm, QL, S) nonzero = attend, or null
+  long long m_sb, m_sh, m_sq;
+  int B, H, S;      // S = number of local cache rows to visit
+  int splits, rows_per_split;
+  float scale_log2;
+  long long q_pos0;  // global position of query row 0, or < 0 for no causal rule
+  long long k_pos0;  // global position of local cache row 0
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// D = head dim (64 or 128), QL = query rows held per CTA.
+template <int D, int QL>
+__global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitParams p) {
+  constexpr int LPR = D / 8;        // lanes per cache row (16 bytes per lane)
+  constexpr int RPW = 32 / LPR;     // rows per warp step
+  constexpr int UNROLL = 4;
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPR, dl = lane % LPR;  // which row of the step, which 8-wide slice of D
+
+  float qf[QL][8];
+#pragma unroll
+  for (int i = 0; i < QL; ++i) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p.q + ((static_cast<long long>(b) * QL + i) * p.H + h) * D + dl * 8);
+    unpack8(u, qf[i]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qf[i][e] *= p.scale_log2;
+  }
+  float acc[QL][8];
+  float m[QL], l[QL];
+#pragma unroll
+  for (int i = 0; i < QL; ++i) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  }
+
+  const int r0 = split * p.rows_per_split;
+  const int r1 = min(p.S, r0 + p.rows_per_split);
+  const __nv_bfloat16* kb = p.k + b * p.k_sb + h * p.k_sh + dl * 8;
+  const __nv_bfloat16* vb = p.v + b * p.v_sb + h * p.v_sh + dl * 8;
+  const int step = WARPS * RPW;
+
+  // The trip count is the same for every lane of a warp (the loop variable ignores `sub`), so the
+  // full-mask shuffles below always see all 32 lanes; rows past the end are merely masked out.
+  for (int base_w = r0 + warp * RPW; base_w < r1; base_w += step * UNROLL) {
+    const int base = base_w + sub;
+    uint4 ku[UNROLL], vu[UNROLL];
+    bool ok[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int r = base + u * step;
+      ok[u] = r < r1;
+      if (ok[u]) {
+        ku[u] = *reinterpret_cast<const uint4*>(kb + static_cast<long long>(r) * p.k_ss);
+        vu[u] = *reinterpret_cast<const uint4*>(vb + static_cast<long long>(r) * p.v_ss);
+      } else {
+        ku[u] = make_uint4(0, 0, 0, 0);
+        vu[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    float s[UNROLL][QL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      float kf[8];
+      unpack8(ku[u], kf);
+      const int r = base + u * step;
+#pragma unroll
+      for (int i = 0; i < QL; ++i) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(qf[i][e], kf[e], d);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        bool vis = ok[u];
+        if (p.q_pos0 >= 0) vis = vis && (p.k_pos0 + r <= p.q_pos0 + i);
+        if (p.mask && vis)
+          vis = p.mask[b * p.m_sb + h * p.m_sh + i * p.m_sq + r] != 0;
+        s[u][i] = vis ? d : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < QL; ++i) {
+      float mx = m[i];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) mx = fmaxf(mx, s[u][i]);
+      const float m_use = mx == -INFINITY ? 0.f : mx;
+      const float alpha = exp2f(m[i] - m_use);  // 0 when m is -inf
+      l[i] *= alpha;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[i][e] *= alpha;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const float pr = exp2f(s[u][i] - m_use);
+        l[i] += pr;
+        float vf[8];
+        unpack8(vu[u], vf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(pr, vf[e], acc[i][e]);
+      }
+      m[i] = mx;
+    }
+  }
+
+  // ---- combine the row groups of a warp, then the warps of the CTA
+  __shared__ float sm_m[WARPS][QL], sm_l[WARPS][QL];
+  __shared__ float sm_o[WARPS][QL][D];
+#pragma unroll
+  for (int i = 0; i < QL; ++i) {
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[i], o);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[i], o);
+      const float mx = fmaxf(m[i], m2);
+      const float mu = mx == -INFINITY ? 0.f : mx;
+      const float a1 = exp2f(m[i] - mu), a2 = exp2f(m2 - mu);
+      l[i] = l[i] * a1 + l2 * a2;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, acc[i][e], o);
+        acc[i][e] = acc[i][e] * a1 + o2 * a2;
+      }
+      m[i] = mx;
+    }
+    if (sub == 0) {
+      if (dl == 0) {
+        sm_m[warp][i] = m[i];
+        sm_l[warp][i] = l[i];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sm_o[warp][i][dl * 8 + e] = acc[i][e];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < QL * D; idx += THREADS) {
+    const int i = idx / D, d = idx % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm_m[w][i]);
+    const float mu = mx == -INFINITY ? 0.f : mx;
+    float lt = 0.f, ot = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float a = exp2f(sm_m[w][i] - mu);
+      lt += sm_l[w][i] * a;
+      ot += sm_o[w][i][d] * a;
+    }
+    const long long pi = ((static_cast<long long>(b) * p.H + h) * QL + i) * p.splits + split;
+    p.o_part[pi * D + d] = lt > 0.f ? ot / lt : 0.f;
+    if (d == 0) p.lse_part[pi] = lt > 0.f ? (mx + log2f(lt)) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+struct MergeParams {
+  const float* o_part;    // element (row, part, d) at row*o_rs + part*o_ps + d
+  const float* lse_part;  // element (row, part) at row*l_rs + part*l_ps
+  long long o_rs, o_ps, l_rs, l_ps;
+  int rows, nparts, D, H, QL;  // QL = 0: rows are already in output order (b, t, h)
+  void* out;              // (B, QL, H, D) bf16 or fp32, or null
+  int out_fp32;
+  float* lse_out;         // (rows) or null
+  // ring variant: store this GPU's merged partial into slot `my_rank` of every rank's inbox
+  float* const* inbox_o;    // [n_ranks] pointers to (rows, n_ranks, D)
+  float* const* inbox_lse;  // [n_ranks] pointers to (rows, n_ranks)
+  int n_ranks, my_rank;
+};
+
+// One CTA per row = (b, h, i); D threads.
+__global__ void decode_merge_kernel(const MergeParams p) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  const float* lp = p.lse_part + static_cast<long long>(row) * p.l_rs;
+  float mx = -INFINITY;
+  for (int s = 0; s < p.nparts; ++s) mx = fmaxf(mx, lp[s * p.l_ps]);
+  float wsum = 0.f, o = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < p.nparts; ++s) {
+      const float w = __expf(lp[s * p.l_ps] - mx);
+      wsum += w;
+      o += w * p.o_part[static_cast<long long>(row) * p.o_rs + s * p.o_ps + d];
+    }
+    o /= wsum;
+  }
+  const float lse = mx == -INFINITY ? -INFINITY : mx + __logf(wsum);
+  if (p.inbox_o) {
+    for (int r = 0; r < p.n_ranks; ++r) {
+      p.inbox_o[r][(static_cast<long long>(row) * p.n_ranks + p.my_rank) * p.D + d] = o;
+      if (d == 0) p.inbox_lse[r][static_cast<long long>(row) * p.n_ranks + p.my_rank] = lse;
+    }
+    __threadfence_system();
+  }
+  if (p.out) {
+    // row = (b*H + h)*QL + i  ->  out[b, i, h, d]
+    long long oi = static_cast<long long>(row) * p.D + d;
+    if (p.QL > 0) {
+      const int i = row % p.QL, h = (row / p.QL) % p.H, b = row / (p.QL * p.H);
+      oi = ((static_cast<long long>(b) * p.QL + i) * p.H + h) * p.D + d;
+    }
+    if (p.out_fp32)
+      reinterpret_cast<float*>(p.out)[oi] = o;
+    else
+      reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16(o);
+  }
+  if (p.lse_out && d == 0) p.lse_out[row] = lse;
+}
+
+// y[M, N] = x[M, K] W[N, K]^T for a handful of rows (M <= 8): one warp per output column, the
+// weight row is read once with 16-byte loads. Bandwidth-bound companion of the tcgen05 GEMM for
+// decode steps, where a 128-row tile would leave most SMs idle.
+template <int M>
+__global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              __nv_bfloat16* __restrict__ y,
+                                                              const __nv_bfloat16* __restrict__ res, int N,
+                                                              int K) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= N) return;
+  float acc[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(warp) * K);
+  for (int c = lane; c < K / 8; c += 32) {
+    float wf[8];
+    unpack8(wr[c], wf);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float xf[8];
+      unpack8(reinterpret_cast<const uint4*>(x + static_cast<long long>(m) * K)[c], xf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+    if (lane == 0) {
+      float v = acc[m];
+      if (res) v += __bfloat162float(res[static_cast<long long>(m) * N + warp]);
+      y[static_cast<long long>(m) * N + warp] = __float2bfloat16(v);
+    }
+  }
+}
+
+}  // namespace decode
+}  // namespace ra
+
+using namespace ra;
+
+struct RaDecodeArgs {
+  const void* q; const void* k; const void* v;
+  long long k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;
+  float* o_part; float* lse_part;
+  const unsigned char* mask; long long m_sb, m_sh, m_sq;
+  int B, H, QL, S, D, splits;
+  float softmax_scale;
+  long long q_pos0, k_pos0;
+  void* stream;
+};
+
+extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
+  using namespace ra::decode;
+  if ((a->D != 64 && a->D != 128) || a->QL < 1 || a->QL > 8 || a->B < 1 || a->H < 1 || a->splits < 1 ||
+      a->S < 0) {
+    set_error("ra_decode_splitkv: head_dim must be 64/128 and 1 <= q_len <= 8");
+    return kHostBadArg;
+  }
+  SplitParams p;
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.k = static_cast<const __nv_bfloat16*>(a->k);
+  p.v = static_cast<const __nv_bfloat16*>(a->v);
+  p.k_sb = a->k_sb; p.k_ss = a->k_ss; p.k_sh = a->k_sh;
+  p.v_sb = a->v_sb; p.v_ss = a->v_ss; p.v_sh = a->v_sh;
+  p.o_part = a->o_part;
+  p.lse_part = a->lse_part;
+  p.mask = a->mask;
+  p.m_sb = a->m_sb; p.m_sh = a->m_sh; p.m_sq = a->m_sq;
+  p.B = a->B; p.H = a->H; p.S = a->S;
+  p.splits = a->splits;
+  p.rows_per_split = (a->S + a->splits - 1) / a->splits;
+  if (p.rows_per_split < 1) p.rows_per_split = 1;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.q_pos0 = a->q_pos0;
+  p.k_pos0 = a->k_pos0;
+  dim3 grid(a->splits, a->H, a->B);
+  cudaStream_t s = static_cast<cudaStream_t>(a->stream);
+#define RA_LAUNCH_DEC(DD, QQ) decode_splitkv_kernel<DD, QQ><<<grid, THREADS, 0, s>>>(p)
+  const int ql = a->QL <= 1 ? 1 : (a->QL <= 2 ? 2 : (a->QL <= 4 ? 4 : 8));
+  if (ql != a->QL) {
+    set_error("ra_decode_splitkv: q_len must be 1, 2, 4 or 8 (pad the query)");
+    return kHostBadArg;
+  }
+  if (a->D == 128) {
+    if (ql == 1) RA_LAUNCH_DEC(128, 1); else if (ql == 2) RA_LAUNCH_DEC(128, 2);
+    else if (ql == 4) RA_LAUNCH_DEC(128, 4); else RA_LAUNCH_DEC(128, 8);
+  } else {
+    if (ql == 1) RA_LAUNCH_DEC(64, 1); else if (ql == 2) RA_LAUNCH_DEC(64, 2);
+    else if (ql == 4) RA_LAUNCH_DEC(64, 4); else RA_LAUNCH_DEC(64, 8);
+  }
+#undef RA_LAUNCH_DEC
+  return check_launch("decode_splitkv_kernel");
+}
+
+extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long long o_rs, long long o_ps,
+                               long long l_rs, long long l_ps, int rows, int nparts, int D, int H,
+                               int QL, void* out, int out_fp32, float* lse_out,
+                               void* const* inbox_o, void* const* inbox_lse, int n_ranks, int my_rank,
+                               void* stream) {
+  using namespace ra::decode;
+  if (rows < 1 || nparts < 1 || (D != 64 && D != 128)) {
+    set_error("ra_decode_merge: bad shape");
+    return kHostBadArg;
+  }
+  MergeParams p;
+  p.o_part = o_part; p.lse_part = lse_part;
+  p.o_rs = o_rs; p.o_ps = o_ps; p.l_rs = l_rs; p.l_ps = l_ps;
+  p.rows = rows; p.nparts = nparts; p.D = D; p.H = H; p.QL = QL;
+  p.out = out; p.out_fp32 = out_fp32; p.lse_out = lse_out;
+  p.inbox_o = reinterpret_cast<float* const*>(inbox_o);
+  p.inbox_lse = reinterpret_cast<float* const*>(inbox_lse);
+  p.n_ranks = n_ranks; p.my_rank = my_rank;
+  decode_merge_kernel<<<rows, D, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("decode_merge_kernel");
+}
+
+extern "C" int ra_small_m_linear(const void* x, const void* w, void* y, const void* res, int M, int N,
+                                 int K, void* stream) {
+  using namespace ra::decode;
+  if (M < 1 || M > 8 || K % 8 || N < 1) {
+    set_error("ra_small_m_linear: need 1 <= M <= 8 and K % 8 == 0");
+    return kHostBadArg;
+  }
+  const int blocks = (N * 32 + 255) / 256;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
+  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
+  switch (M) {
+    case 1: small_m_linear_kernel<1><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 2: small_m_linear_kernel<2><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 3: small_m_linear_kernel<3><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 4: small_m_linear_kernel<4><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 5: small_m_linear_kernel<5><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 6: small_m_linear_kernel<6><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    case 7: small_m_linear_kernel<7><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+    default: small_m_linear_kernel<8><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
+  }
+  return check_launch("small_m_linear_kernel");
+}

@@ -1,0 +1,199 @@
+"""Long-context inference on the LLaMA driver: sequence-sharded KV cache, chunked prefill and
+greedy decoding.
+
+Cache layout follows the reference's inference contract (ringattention_inference.py:19-20,
+ringattention_jax.py:34-35): rank r of the ``sp`` axis owns the contiguous positions
+``[r * S_max, (r + 1) * S_max)``. The cache never moves:
+
+* prefill: the chunk's tokens are split over the ranks for the dense layers; queries are
+  all-gathered (small), every rank runs the flash kernel against *its own* cache rows, and the
+  per-rank ``(o, lse)`` partials are exchanged and merged;
+* decode: the tiny dense layers are computed redundantly on every rank (weights are replicated),
+  attention runs the split-KV kernel on the local shard and merges across GPUs through peer stores.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import LlamaConfig
+from ..ops import attention as A
+from ..ops import decode as Dk
+from ..ops import flash
+from ..ops import kernels as K
+from ..ops.flash import MaskSpec, Positions
+from ..parallel.mesh import AxisContext, resolve_axis
+from .llama import FlatParams
+
+
+class LlamaInference:
+    def __init__(self, cfg: LlamaConfig, max_context: int, batch: int = 1, device="cuda", seed: int = 0,
+                 axis: "AxisContext | str | None" = None, params: Optional[FlatParams] = None,
+                 symm_ring=None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.axis = resolve_axis(axis)
+        self.rank, self.world = self.axis.rank, self.axis.size
+        self.group = self.axis.group
+        self.symm_ring = symm_ring
+        if self.world > 1 and symm_ring is None:
+            from ..parallel.symm import SymmRing
+
+            self.symm_ring = SymmRing(self.group, self.device)
+        self.params = params if params is not None else FlatParams(cfg, self.device, seed, with_optimizer=False)
+        self.B = batch
+        self.H, self.D, self.d = cfg.n_heads, cfg.head_dim, cfg.d_model
+        if max_context % (self.world * 128):
+            raise ValueError("max_context must be a multiple of 128 * sp")
+        self.S_max = max_context // self.world      # cache rows per rank
+        self.k0 = self.rank * self.S_max            # global position of local row 0
+        self.cache = [torch.zeros(batch, self.S_max, 2, self.H, self.D, device=self.device, dtype=torch.bfloat16)
+                      for _ in range(cfg.n_layers)]
+        self.length = 0                             # tokens in the cache (global)
+
+    # ------------------------------------------------------------------ helpers
+    def _n_local(self, total: int) -> int:
+        return max(0, min(self.S_max, total - self.k0))
+
+    def _store_kv(self, layer: int, k: torch.Tensor, v: torch.Tensor, pos0: int) -> None:
+        """``k, v (B, T, H, D)`` for global positions ``[pos0, pos0+T)``: keep the part this rank owns."""
+        T = k.shape[1]
+        lo, hi = max(pos0, self.k0), min(pos0 + T, self.k0 + self.S_max)
+        if lo < hi:
+            c = self.cache[layer]
+            c[:, lo - self.k0:hi - self.k0, 0].copy_(k[:, lo - pos0:hi - pos0])
+            c[:, lo - self.k0:hi - self.k0, 1].copy_(v[:, lo - pos0:hi - pos0])
+
+    def _gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        """All-gather along the token dim (dim 1) of a ``(B, t, ...)`` tensor over the sp axis."""
+        if self.world == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill_chunk(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Append a chunk ``tokens (B, Tc)`` (identical on all ranks, ``Tc`` divisible by 128*sp) to
+        the cache. Returns the last position's logits ``(B, vocab)`` fp32 on every rank."""
+        cfg, P = self.cfg, self.params
+        B, Tc = tokens.shape
+        N, H, D, d = self.world, self.H, self.D, self.d
+        if Tc % (N * 128):
+            raise ValueError("chunk length must be a multiple of 128 * sp")
+        t = Tc // N
+        pos0 = self.length
+        mypos = Positions(pos0 + self.rank * t)
+        tok = tokens[:, self.rank * t:(self.rank + 1) * t].to(self.device, torch.int32).contiguous()
+        x = K.embedding_fwd(tok.reshape(-1), P.w("embed"))
+        n_after = self._n_local(pos0 + Tc)
+        for l in range(cfg.n_layers):
+            h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
+            qkv = K.linear_fwd(h1, P.w(f"l{l}.wqkv"))
+            K.rope_(qkv.view(B, t, 3 * H, D)[:, :, :2 * H], mypos, cfg.rope_theta)
+            qkv5 = qkv.view(B, t, 3, H, D)
+            kv_all = self._gather_tokens(qkv5[:, :, 1:3].contiguous())       # (B, Tc, 2, H, D)
+            self._store_kv(l, kv_all[:, :, 0], kv_all[:, :, 1], pos0)
+            q_all = self._gather_tokens(qkv5[:, :, 0].contiguous())          # (B, Tc, H, D)
+            c = self.cache[l]
+            if n_after > 0:
+                ms = MaskSpec(causal_block_size=cfg.causal_block_size, q_pos=Positions(pos0),
+                              k_pos=Positions(self.k0))
+                o_p, lse_p = flash.flash_fwd(q_all, c[:, :n_after, 0], c[:, :n_after, 1], ms, out_fp32=(N > 1))
+            else:
+                o_p = torch.zeros(B, Tc, H, D, device=self.device, dtype=torch.float32)
+                lse_p = torch.full((B, H, Tc), float("-inf"), device=self.device)
+            if N == 1:
+                attn = o_p
+            else:
+                attn = self._merge_prefill(o_p, lse_p, t)
+            x = K.linear_fwd(attn.reshape(B * t, d), P.w(f"l{l}.wo"), residual=x)
+            h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
+            step = min(cfg.ffn_chunk_size, B * t)
+            x3 = torch.empty_like(x)
+            for r0 in range(0, B * t, step):
+                r1 = min(B * t, r0 + step)
+                gu = K.linear_fwd(h2[r0:r1], P.w(f"l{l}.wgu"))
+                K.linear_fwd(K.swiglu_fwd(gu), P.w(f"l{l}.wd"), out=x3[r0:r1], residual=x[r0:r1])
+            x = x3
+        self.length = pos0 + Tc
+        # logits of the globally last token live on the last rank; share them
+        last = x.view(B, t, d)[:, -1].contiguous()
+        hf, _ = K.rmsnorm_fwd(last, P.w("nf"), cfg.rms_eps)
+        logits = K.small_m_linear(hf, P.w("lm_head")).float() if B <= 8 else K.linear_fwd(hf, P.w("lm_head")).float()
+        if N > 1:
+            dist.broadcast(logits, dist.get_global_rank(self.group, N - 1), group=self.group)
+        return logits
+
+    def _merge_prefill(self, o_p: torch.Tensor, lse_p: torch.Tensor, t: int) -> torch.Tensor:
+        """Exchange per-rank partials so that every rank holds the N partials of its own ``t`` query
+        rows, then merge them with the log-sum-exp kernel."""
+        N, B, H, D = self.world, o_p.shape[0], self.H, self.D
+        lse_bth = lse_p.permute(0, 2, 1).contiguous()                          # (B, Tc, H)
+        send_o = o_p.view(B, N, t, H, D).permute(1, 0, 2, 3, 4).contiguous()   # (N, B, t, H, D)
+        send_l = lse_bth.view(B, N, t, H).permute(1, 0, 2, 3).contiguous()     # (N, B, t, H)
+        recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
+        dist.all_to_all_single(recv_o, send_o, group=self.group)
+        dist.all_to_all_single(recv_l, send_l, group=self.group)
+        rows = B * t * H
+        out = torch.empty(B, t, H, D, device=self.device, dtype=torch.bfloat16)
+        Dk.merge_partials(recv_o.view(N, rows, D).permute(1, 0, 2), recv_l.view(N, rows).permute(1, 0),
+                          H, 0, out=out)
+        return out
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One token per sequence: ``tokens (B,)`` -> logits ``(B, vocab)`` fp32 (same on all ranks)."""
+        cfg, P = self.cfg, self.params
+        B, H, D, d = self.B, self.H, self.D, self.d
+        pos = self.length
+        x = K.embedding_fwd(tokens.to(self.device, torch.int32).reshape(-1).contiguous(), P.w("embed"))
+        n_local = self._n_local(pos + 1)
+        for l in range(cfg.n_layers):
+            h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
+            qkv = K.linear_auto(h1, P.w(f"l{l}.wqkv"))
+            K.rope_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], Positions(pos), cfg.rope_theta)
+            qkv5 = qkv.view(B, 1, 3, H, D)
+            self._store_kv(l, qkv5[:, :, 1], qkv5[:, :, 2], pos)
+            c = self.cache[l]
+            attn = Dk.ring_decode_attention(qkv5[:, :, 0].contiguous(), c[:, :, 0], c[:, :, 1], None, self.axis,
+                                            self.symm_ring, n_valid=n_local, q_pos0=pos, k_pos0=self.k0)
+            x = K.linear_auto(attn.reshape(B, d), P.w(f"l{l}.wo"), residual=x)
+            h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
+            gu = K.linear_auto(h2, P.w(f"l{l}.wgu"))
+            x = K.linear_auto(K.swiglu_fwd(gu), P.w(f"l{l}.wd"), residual=x)
+        self.length = pos + 1
+        hf, _ = K.rmsnorm_fwd(x, P.w("nf"), cfg.rms_eps)
+        return K.linear_auto(hf, P.w("lm_head")).float()
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, new_tokens: int, chunk: int = 32768):
+        """Chunked prefill of ``prompt (B, T)`` followed by greedy decoding. Returns the generated
+        tokens ``(B, new_tokens)`` and timing: prefill seconds, per-token decode latencies."""
+        B, T = prompt.shape
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        logits = None
+        for c0 in range(0, T, chunk):
+            logits = self.prefill_chunk(prompt[:, c0:c0 + chunk])
+        torch.cuda.synchronize()
+        t_prefill = time.perf_counter() - t0
+        out: List[torch.Tensor] = []
+        lat: List[float] = []
+        nxt = logits.argmax(dim=-1)
+        for _ in range(new_tokens):
+            out.append(nxt)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            logits = self.decode_step(nxt)
+            nxt = logits.argmax(dim=-1)
+            e1.record()
+            torch.cuda.synchronize()
+            lat.append(e0.elapsed_time(e1))
+        return torch.stack(out, dim=1), {"prefill_s": t_prefill, "decode_ms": lat}

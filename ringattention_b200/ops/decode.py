@@ -1,0 +1,145 @@
+"""Decode attention with a stationary, sequence-sharded KV cache (``decode_sm100.cu``).
+
+``ring_decode_attention`` is the fused path of ``ringattention_inference``
+(ringattention/ringattention_inference.py:8-35 rotates the whole cache; here only ``(o, lse)``
+partials of ``B*H*q_len*(D+1)`` floats per rank cross NVLink, by stores into the peers' inboxes).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+c_ll = ctypes.c_longlong
+c_vp = ctypes.c_void_p
+
+
+class _DecodeArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_vp), ("k", c_vp), ("v", c_vp),
+        ("k_sb", c_ll), ("k_ss", c_ll), ("k_sh", c_ll), ("v_sb", c_ll), ("v_ss", c_ll), ("v_sh", c_ll),
+        ("o_part", c_vp), ("lse_part", c_vp),
+        ("mask", c_vp), ("m_sb", c_ll), ("m_sh", c_ll), ("m_sq", c_ll),
+        ("B", ctypes.c_int), ("H", ctypes.c_int), ("QL", ctypes.c_int), ("S", ctypes.c_int),
+        ("D", ctypes.c_int), ("splits", ctypes.c_int),
+        ("softmax_scale", ctypes.c_float),
+        ("q_pos0", c_ll), ("k_pos0", c_ll),
+        ("stream", c_vp),
+    ]
+
+
+def _pad_q(q: torch.Tensor):
+    """Pad the query length to 1, 2, 4 or 8 rows (the kernel holds them in registers)."""
+    ql = q.shape[1]
+    if ql > 8:
+        raise ValueError("decode attention handles at most 8 query rows per call; use the prefill path")
+    tgt = 1 if ql == 1 else (2 if ql == 2 else (4 if ql <= 4 else 8))
+    if tgt != ql:
+        pad = torch.zeros(q.shape[0], tgt - ql, q.shape[2], q.shape[3], device=q.device, dtype=q.dtype)
+        q = torch.cat([q, pad], dim=1)
+    return q.contiguous(), ql, tgt
+
+
+def default_splits(S: int, B: int, H: int) -> int:
+    """Enough CTAs to fill the GPU a few times over, at least 256 cache rows per CTA."""
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    want = max(1, (4 * sms) // max(1, B * H))
+    return max(1, min(want, (S + 255) // 256, 512))
+
+
+def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, k_pos0: int = 0,
+                   mask: Optional[torch.Tensor] = None, splits: Optional[int] = None):
+    """Split-KV pass over this rank's cache rows ``[0, n_valid)``. Returns fp32 partials
+    ``(o_part (B*H*QL, splits, D), lse_part (B*H*QL, splits), QL_padded)``."""
+    B, QL, H, D = q.shape
+    S = k.shape[1] if n_valid is None else int(n_valid)
+    splits = splits or default_splits(S, B, H)
+    rows = B * H * QL
+    o_part = torch.empty(rows, splits, D, device=q.device, dtype=torch.float32)
+    lse_part = torch.empty(rows, splits, device=q.device, dtype=torch.float32)
+    a = _DecodeArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.k_sb, a.k_ss, a.k_sh = k.stride(0), k.stride(1), k.stride(2)
+    a.v_sb, a.v_ss, a.v_sh = v.stride(0), v.stride(1), v.stride(2)
+    a.o_part, a.lse_part = o_part.data_ptr(), lse_part.data_ptr()
+    if mask is not None:
+        assert mask.dtype == torch.uint8 and mask.dim() == 4 and mask.stride(3) == 1
+        a.mask = mask.data_ptr()
+        a.m_sb = mask.stride(0) if mask.shape[0] > 1 else 0
+        a.m_sh = mask.stride(1) if mask.shape[1] > 1 else 0
+        a.m_sq = mask.stride(2) if mask.shape[2] > 1 else 0
+    a.B, a.H, a.QL, a.S, a.D, a.splits = B, H, QL, S, D, splits
+    a.softmax_scale = 1.0 / math.sqrt(D)
+    a.q_pos0, a.k_pos0 = int(q_pos0), int(k_pos0)
+    a.stream = torch.cuda.current_stream().cuda_stream
+    _lib.call("ra_decode_splitkv", ctypes.byref(a))
+    return o_part, lse_part
+
+
+def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None, inbox=None):
+    """Merge ``nparts`` partials per row; ``o_part (rows, nparts, D)`` and ``lse_part (rows, nparts)``
+    may be strided views. ``QL = 0`` writes rows in their own order (prefill); ``QL > 0`` maps row
+    ``(b, h, i)`` to ``out[b, i, h]`` (decode). ``inbox = (o_ptrs, lse_ptrs, n_ranks, my_rank)`` makes the
+    kernel also store the merged row into slot ``my_rank`` of every rank's inbox."""
+    rows, nparts, D = o_part.shape
+    assert o_part.stride(2) == 1
+    o_ptrs = lse_ptrs = 0
+    n_ranks = my_rank = 0
+    if inbox is not None:
+        o_ptrs, lse_ptrs, n_ranks, my_rank = inbox
+    _lib.call("ra_decode_merge", c_vp(o_part.data_ptr()), c_vp(lse_part.data_ptr()),
+              c_ll(o_part.stride(0)), c_ll(o_part.stride(1)), c_ll(lse_part.stride(0)),
+              c_ll(lse_part.stride(1)), rows, nparts, D, H, QL,
+              c_vp(0 if out is None else out.data_ptr()),
+              0 if out is None else int(out.dtype == torch.float32),
+              c_vp(0 if lse_out is None else lse_out.data_ptr()), c_vp(o_ptrs), c_vp(lse_ptrs),
+              n_ranks, my_rank, _lib.stream_ptr())
+    return out
+
+
+def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: Optional[int] = None,
+                          q_pos0: int = -1, k_pos0: Optional[int] = None):
+    """``q (B, q_len<=8, H, D)`` replicated; ``k, v (B, kv_len, H, D)`` local cache shard; boolean
+    ``attn_mask`` broadcastable to ``(B, H, q_len, S_total)``, global on the last axis (True =
+    attend). Returns ``(B, q_len, H, D)`` in ``v.dtype``, identical on every rank."""
+    rank, world = axis.rank, axis.size
+    B, ql, H, D = q.shape
+    S_loc = k.shape[1]
+    qp, ql, QL = _pad_q(q)
+    mask_u8 = None
+    if attn_mask is not None:
+        m = attn_mask
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m = m[..., rank * S_loc:(rank + 1) * S_loc]
+        if m.shape[2] not in (1, QL):
+            pad = torch.zeros(*m.shape[:2], QL - m.shape[2], m.shape[3], dtype=m.dtype, device=m.device)
+            m = torch.cat([m, pad], dim=2)
+        mask_u8 = m.to(torch.uint8).contiguous()
+    if k_pos0 is None:
+        k_pos0 = rank * S_loc
+    o_part, lse_part = decode_partial(qp, k, v, n_valid=n_valid, q_pos0=q_pos0, k_pos0=k_pos0, mask=mask_u8)
+    out = torch.empty(B, QL, H, D, device=q.device, dtype=v.dtype)
+    if world == 1:
+        merge_partials(o_part, lse_part, H, QL, out=out)
+        return out[:, :ql]
+    if symm_ring is None:
+        raise RuntimeError("multi-rank decode needs a symmetric-memory ring")
+    rows = B * H * QL
+    inbox_o = symm_ring.buffer("decode_inbox_o", 2 * rows * world * D * 4)
+    inbox_l = symm_ring.buffer("decode_inbox_lse", 2 * rows * world * 4)
+    slot = symm_ring.calls & 1  # double-buffered across calls: one barrier per call is enough
+    symm_ring.calls += 1
+    off_o, off_l = slot * rows * world * D * 4, slot * rows * world * 4
+    o_ptrs = torch.tensor([p + off_o for p in inbox_o.peer_ptrs], dtype=torch.int64, device=q.device)
+    l_ptrs = torch.tensor([p + off_l for p in inbox_l.peer_ptrs], dtype=torch.int64, device=q.device)
+    merge_partials(o_part, lse_part, H, QL, inbox=(o_ptrs.data_ptr(), l_ptrs.data_ptr(), world, rank))
+    symm_ring.barrier()
+    io = inbox_o.local[off_o:off_o + rows * world * D * 4].view(torch.float32).view(rows, world, D)
+    il = inbox_l.local[off_l:off_l + rows * world * 4].view(torch.float32).view(rows, world)
+    merge_partials(io, il, H, QL, out=out)
+    return out[:, :ql]

@@ -192,3 +192,24 @@ def cast_bf16_to_f32(src, dst):
     assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
     _lib.call("ra_cast_bf16_f32", ptr(src), ptr(dst), c_ll(src.numel()), stream_ptr())
     return dst
+
+
+def small_m_linear(x, w, out=None, residual=None):
+    """``y = x W^T (+ residual)`` for at most 8 rows: a bandwidth-bound kernel that reads every weight
+    row once (decode steps). ``x (M,K)``, ``w (N,K)`` bf16 contiguous."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    assert x.is_contiguous() and w.is_contiguous() and M <= 8
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    assert out.is_contiguous() and (residual is None or residual.is_contiguous())
+    _lib.call("ra_small_m_linear", ptr(x), ptr(w), ptr(out), ptr(residual), M, N, Kd, stream_ptr())
+    return out
+
+
+def linear_auto(x, w, out=None, residual=None):
+    """Pick the tcgen05 GEMM or the small-M kernel by the number of rows."""
+    if x.shape[0] <= 8 and x.is_contiguous() and (out is None or out.is_contiguous()) and \
+            (residual is None or residual.is_contiguous()):
+        return small_m_linear(x, w, out=out, residual=residual)
+    return linear_fwd(x, w, out=out, residual=residual)
