@@ -1,0 +1,81 @@
+"""Tracing helpers: NVTX ranges around host-side phases and the in-kernel phase timestamps of the
+attention backward.
+
+The reference only wraps its two TPU backward launches in ``jax.named_scope``
+(ringattention_pallas_tpu.py:1232-1235,1615-1616). Here every phase of a training step can be put
+in an NVTX range (visible to any CUDA profiler), and the backward kernel can record SM-clock
+timestamps of its pipeline hand-offs for one CTA, which is how the overlap of MMA, softmax and dQ
+reduction is measured without a profiler.
+"""
+from __future__ import annotations
+
+import contextlib
+import ctypes
+import os
+
+import torch
+
+_ENABLED = os.environ.get("RINGATTN_B200_NVTX", "0") == "1"
+
+
+def enable_nvtx(on: bool = True) -> None:
+    global _ENABLED
+    _ENABLED = on
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """NVTX range when tracing is enabled (``RINGATTN_B200_NVTX=1`` or :func:`enable_nvtx`)."""
+    if _ENABLED and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
+ROLES = ("mma", "softmax", "drain")
+SLOTS = {
+    "mma": ("dP issued", "p_ready seen", "ds_ready seen", "iteration issued"),
+    "softmax": ("s_full seen", "p_ready arrived", "dp_full seen", "ds_ready arrived"),
+    "drain": ("dq_full seen", "dq_empty arrived", "staging done", "-"),
+}
+
+
+class BackwardPhaseTrace:
+    """Collect phase timestamps of the first compute CTA of the next attention-backward launches.
+
+    >>> with BackwardPhaseTrace() as tr:
+    ...     flash.flash_bwd(...)
+    >>> tr.cycles_per_iteration()
+    """
+
+    def __init__(self):
+        from ..ops import _lib
+
+        self._lib = _lib.lib()
+        self.buf = torch.zeros(4, 64, 4, dtype=torch.int64, device="cuda")
+
+    def __enter__(self):
+        self._lib.ra_set_bwd_trace(ctypes.c_void_p(self.buf.data_ptr()))
+        return self
+
+    def __exit__(self, *exc):
+        torch.cuda.synchronize()
+        self._lib.ra_set_bwd_trace(ctypes.c_void_p(0))
+        self.table = self.buf.cpu()
+        return False
+
+    def cycles_per_iteration(self, first: int = 8, last: int = 40) -> float:
+        t = self.table
+        return float(t[0, last, 0] - t[0, first, 0]) / (last - first)
+
+    def rows(self, first: int = 8, count: int = 8):
+        t = self.table
+        base = int(t[0, first, 0])
+        out = []
+        for it in range(first, first + count):
+            out.append({role: [int(t[r, it, s]) - base for s in range(4)] for r, role in enumerate(ROLES)})
+        return out
