@@ -13,7 +13,6 @@ per-layer activations that backward needs.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -24,86 +23,7 @@ from ..ops import attention as A
 from ..ops import kernels as K
 from ..ops.flash import Positions
 from ..ops.reference import shard_segments
-
-
-class FlatParams:
-    """Flat parameter storage. Matrices come first (weight decay applies to ``[0, decay_end)``),
-    norm gains last. ``shard`` = (index, count) keeps only a contiguous 1/count slice of the
-    optimizer state (fp32 master, moments); the bf16 working copy and the grads stay full-size."""
-
-    def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
-                 shard: Tuple[int, int] = (0, 1)):
-        self.cfg = cfg
-        self.device = device
-        d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
-        self.index: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
-        off = 0
-
-        def add(name, shape):
-            nonlocal off
-            n = math.prod(shape)
-            self.index[name] = (off, shape)
-            off += (n + 63) // 64 * 64  # keep every tensor 256-byte aligned in bf16 and fp32
-
-        add("embed", (V, d))
-        for l in range(cfg.n_layers):
-            add(f"l{l}.wqkv", (3 * d, d))
-            add(f"l{l}.wo", (d, d))
-            add(f"l{l}.wgu", (2 * F, d))
-            add(f"l{l}.wd", (d, F))
-        add("lm_head", (V, d))
-        self.decay_end = off
-        for l in range(cfg.n_layers):
-            add(f"l{l}.n1", (d,))
-            add(f"l{l}.n2", (d,))
-        add("nf", (d,))
-        self.numel = (off + 1023) // 1024 * 1024
-        self.shard_index, self.shard_count = shard
-        if self.numel % (self.shard_count * 4):
-            self.numel = (self.numel + self.shard_count * 1024 - 1) // (self.shard_count * 1024) * (self.shard_count * 1024)
-        self.p16 = torch.empty(self.numel, device=device, dtype=torch.bfloat16)
-        self.g32: Optional[torch.Tensor] = None
-        self._init_weights(seed)
-        self.p32 = self.m = self.v = None
-        if with_optimizer:
-            lo, hi = self.shard_range()
-            self.p32 = self.p16[lo:hi].float()
-            self.m = torch.zeros(hi - lo, device=device, dtype=torch.float32)
-            self.v = torch.zeros(hi - lo, device=device, dtype=torch.float32)
-
-    def shard_range(self) -> Tuple[int, int]:
-        n = self.numel // self.shard_count
-        return self.shard_index * n, (self.shard_index + 1) * n
-
-    def _init_weights(self, seed: int) -> None:
-        gen = torch.Generator(device=self.device)
-        gen.manual_seed(seed)
-        self.p16.zero_()
-        chunk = 1 << 26
-        # N(0, init_std) for matrices, drawn in fp32 chunks to bound peak memory
-        for s0 in range(0, self.decay_end, chunk):
-            n = min(chunk, self.decay_end - s0)
-            self.p16[s0:s0 + n] = (torch.randn(n, device=self.device, generator=gen) * self.cfg.init_std).bfloat16()
-        self.p16[self.decay_end:] = 0
-        for name, (off, shape) in self.index.items():
-            if len(shape) == 1:
-                self.p16[off:off + shape[0]] = 1.0
-
-    def ensure_grads(self) -> torch.Tensor:
-        if self.g32 is None:
-            self.g32 = torch.zeros(self.numel, device=self.device, dtype=torch.float32)
-        return self.g32
-
-    def w(self, name: str) -> torch.Tensor:
-        off, shape = self.index[name]
-        return self.p16[off:off + math.prod(shape)].view(shape)
-
-    def g(self, name: str) -> torch.Tensor:
-        off, shape = self.index[name]
-        return self.g32[off:off + math.prod(shape)].view(shape)
-
-    def n_params(self) -> int:
-        return sum(math.prod(s) for _, s in self.index.values())
+from .params import FlatParams
 
 
 @dataclass
@@ -148,13 +68,13 @@ class LlamaModel:
         cfg, P = self.cfg, self.params
         B, S, H, D, d = ctx.B, ctx.S, self.H, self.D, cfg.d_model
         h1, rstd1 = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
-        qkv = K.linear_fwd(h1, P.w(f"l{l}.wqkv"))
+        qkv = P.lin_fwd(h1, f"l{l}.wqkv")
         qkv5 = qkv.view(B, S, 3, H, D)
         qk = qkv.view(B, S, 3 * H, D)[:, :, :2 * H]  # q heads then k heads
         K.rope_(qk, ctx.positions, cfg.rope_theta)
         q, k, v = qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]
         attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
-        x2 = K.linear_fwd(attn.view(B * S, d), P.w(f"l{l}.wo"), residual=x)
+        x2 = P.lin_fwd(attn.view(B * S, d), f"l{l}.wo", residual=x)
         return x2, (h1, rstd1, qkv, attn, lse)
 
     def _ffn_fwd(self, l: int, x2: torch.Tensor, h2: torch.Tensor) -> torch.Tensor:
@@ -162,12 +82,11 @@ class LlamaModel:
         M = x2.shape[0]
         x3 = torch.empty_like(x2)
         step = min(cfg.ffn_chunk_size, M)
-        wgu, wd = P.w(f"l{l}.wgu"), P.w(f"l{l}.wd")
         for r0 in range(0, M, step):
             r1 = min(M, r0 + step)
-            gu = K.linear_fwd(h2[r0:r1], wgu)
+            gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
             a = K.swiglu_fwd(gu)
-            K.linear_fwd(a, wd, out=x3[r0:r1], residual=x2[r0:r1])
+            P.lin_fwd(a, f"l{l}.wd", out=x3[r0:r1], residual=x2[r0:r1])
         return x3
 
     def layer_forward(self, l: int, x: torch.Tensor, ctx: StepContext, keep: bool = False):
@@ -188,33 +107,32 @@ class LlamaModel:
             h2, rstd2 = K.rmsnorm_fwd(x2, P.w(f"l{l}.n2"), cfg.rms_eps)
             saved = s + (x2, h2, rstd2)
         h1, rstd1, qkv, attn, lse, x2, h2, rstd2 = saved
-        wgu, wd = P.w(f"l{l}.wgu"), P.w(f"l{l}.wd")
         # ---- blockwise FFN backward (each chunk recomputes its activations)
         dh2 = torch.empty_like(x2)
         step = min(cfg.ffn_chunk_size, M)
         for r0 in range(0, M, step):
             r1 = min(M, r0 + step)
-            gu = K.linear_fwd(h2[r0:r1], wgu)
+            gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
             a = K.swiglu_fwd(gu)
-            da = K.linear_dgrad(dx3[r0:r1], wd)
-            K.linear_wgrad(dx3[r0:r1], a, P.g(f"l{l}.wd"))
+            da = P.lin_dgrad(dx3[r0:r1], f"l{l}.wd")
+            P.lin_wgrad(dx3[r0:r1], a, f"l{l}.wd")
             K.swiglu_bwd_(gu, da)
-            K.linear_wgrad(gu, h2[r0:r1], P.g(f"l{l}.wgu"))
-            K.linear_dgrad(gu, wgu, out=dh2[r0:r1])
+            P.lin_wgrad(gu, h2[r0:r1], f"l{l}.wgu")
+            P.lin_dgrad(gu, f"l{l}.wgu", out=dh2[r0:r1])
         dx2 = K.rmsnorm_bwd(dh2, x2, P.w(f"l{l}.n2"), rstd2, P.g(f"l{l}.n2"), dres=dx3)
         del dh2
         # ---- attention block backward
         attn2 = attn.view(M, d)
-        dattn = K.linear_dgrad(dx2, P.w(f"l{l}.wo"))
-        K.linear_wgrad(dx2, attn2, P.g(f"l{l}.wo"))
+        dattn = P.lin_dgrad(dx2, f"l{l}.wo")
+        P.lin_wgrad(dx2, attn2, f"l{l}.wo")
         qkv5 = qkv.view(B, S, 3, H, D)
         dqkv = torch.empty_like(qkv)
         dqkv5 = dqkv.view(B, S, 3, H, D)
         A.ring_backward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], attn, lse, dattn.view(B, S, H, D),
                         ctx.plan, ctx.symm_ring, dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
         K.rope_(dqkv.view(B, S, 3 * H, D)[:, :, :2 * H], ctx.positions, cfg.rope_theta, inverse=True)
-        K.linear_wgrad(dqkv, h1, P.g(f"l{l}.wqkv"))
-        dh1 = K.linear_dgrad(dqkv, P.w(f"l{l}.wqkv"))
+        P.lin_wgrad(dqkv, h1, f"l{l}.wqkv")
+        dh1 = P.lin_dgrad(dqkv, f"l{l}.wqkv")
         dx = K.rmsnorm_bwd(dh1, x, P.w(f"l{l}.n1"), rstd1, P.g(f"l{l}.n1"), dres=dx2)
         return dx
 
@@ -227,18 +145,17 @@ class LlamaModel:
         M = x.shape[0]
         hf, rstdf = K.rmsnorm_fwd(x, P.w("nf"), cfg.rms_eps)
         dhf = torch.empty_like(x) if compute_grad else None
-        wlm = P.w("lm_head")
         losses = torch.empty(M, device=x.device, dtype=torch.float32)
         step = min(cfg.loss_chunk_size, M)
         scale = 1.0 / max(1, ctx.total_tokens)
         tflat = targets.reshape(-1)
         for r0 in range(0, M, step):
             r1 = min(M, r0 + step)
-            logits = K.linear_fwd(hf[r0:r1], wlm)
+            logits = P.lin_fwd(hf[r0:r1], "lm_head")
             K.xent_fwd_bwd_(logits, tflat[r0:r1], scale, loss=losses[r0:r1])
             if compute_grad:
-                K.linear_wgrad(logits, hf[r0:r1], P.g("lm_head"))
-                K.linear_dgrad(logits, wlm, out=dhf[r0:r1])
+                P.lin_wgrad(logits, hf[r0:r1], "lm_head")
+                P.lin_dgrad(logits, "lm_head", out=dhf[r0:r1])
         loss_sum = losses.sum()
         if not compute_grad:
             return loss_sum, None

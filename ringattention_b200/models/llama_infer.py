@@ -27,7 +27,7 @@ from ..ops import flash
 from ..ops import kernels as K
 from ..ops.flash import MaskSpec, Positions
 from ..parallel.mesh import AxisContext, resolve_axis
-from .llama import FlatParams
+from .params import FlatParams
 
 
 class LlamaInference:
@@ -94,7 +94,7 @@ class LlamaInference:
         n_after = self._n_local(pos0 + Tc)
         for l in range(cfg.n_layers):
             h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
-            qkv = K.linear_fwd(h1, P.w(f"l{l}.wqkv"))
+            qkv = P.lin_fwd(h1, f"l{l}.wqkv")
             K.rope_(qkv.view(B, t, 3 * H, D)[:, :, :2 * H], mypos, cfg.rope_theta)
             qkv5 = qkv.view(B, t, 3, H, D)
             kv_all = self._gather_tokens(qkv5[:, :, 1:3].contiguous())       # (B, Tc, 2, H, D)
@@ -112,14 +112,14 @@ class LlamaInference:
                 attn = o_p
             else:
                 attn = self._merge_prefill(o_p, lse_p, t)
-            x = K.linear_fwd(attn.reshape(B * t, d), P.w(f"l{l}.wo"), residual=x)
+            x = P.lin_fwd(attn.reshape(B * t, d), f"l{l}.wo", residual=x)
             h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
             step = min(cfg.ffn_chunk_size, B * t)
             x3 = torch.empty_like(x)
             for r0 in range(0, B * t, step):
                 r1 = min(B * t, r0 + step)
-                gu = K.linear_fwd(h2[r0:r1], P.w(f"l{l}.wgu"))
-                K.linear_fwd(K.swiglu_fwd(gu), P.w(f"l{l}.wd"), out=x3[r0:r1], residual=x[r0:r1])
+                gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
+                P.lin_fwd(K.swiglu_fwd(gu), f"l{l}.wd", out=x3[r0:r1], residual=x[r0:r1])
             x = x3
         self.length = pos0 + Tc
         # logits of the globally last token live on the last rank; share them

@@ -1,0 +1,263 @@
+"""Parameter storage of the LLaMA driver: flat buffers, optional row-sharding over an ``fsdp`` group.
+
+All GEMM weights ``W[N][K]`` are split by rows into ``f`` shards of ``shard_rows = ceil(N/f/256)*256``
+rows (``f = 1``: the whole matrix). The buffers are *shard-major*: the shard of rank r of every matrix
+is contiguous, so the optimizer state a rank owns (fp32 master, moments) is one slice and AdamW is one
+launch. Embedding table and norm gains are replicated.
+
+With ``f > 1`` the bf16 working copy of a rank's shard lives in symmetric memory; the other ranks never
+hold a gathered copy of the model. ``lin_fwd`` / ``lin_dgrad`` run the GEMM whose leading CTAs pull the
+remote shards into a scratch while the rest of the grid already computes on the local rows
+(``csrc/gemm_gather_sm100.cu``) - the parameter all-gather is fused into the GEMM that consumes the
+weights. ``lin_wgrad`` produces the full weight gradient shard by shard; gradients are all-reduced by
+the trainer and every rank applies only its own rows.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..config import LlamaConfig
+from ..ops import _lib
+from ..ops import kernels as K
+
+c_ll = ctypes.c_longlong
+c_vp = ctypes.c_void_p
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatParams:
+    def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
+                 shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 24):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.shard_index, self.shard_count = shard
+        self.fsdp_group = fsdp_group
+        self.gather_ctas = gather_ctas
+        f = self.shard_count
+        d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+
+        # ---- layout
+        self.mat: Dict[str, Tuple[int, int, int, int]] = {}   # name -> (offset in shard, N, K, shard_rows)
+        self.rep: Dict[str, Tuple[int, Tuple[int, ...]]] = {}  # name -> (offset in replicated region, shape)
+        off = 0
+        mats: List[Tuple[str, int, int]] = []
+        for l in range(cfg.n_layers):
+            mats += [(f"l{l}.wqkv", 3 * d, d), (f"l{l}.wo", d, d), (f"l{l}.wgu", 2 * F, d), (f"l{l}.wd", d, F)]
+        mats.append(("lm_head", V, d))
+        for name, N, Kd in mats:
+            sr = N if f == 1 else _round_up((N + f - 1) // f, 256)
+            self.mat[name] = (off, N, Kd, sr)
+            off += _round_up(sr * Kd, 64)
+        self.numel_shard = _round_up(off, 1024)
+        off = 0
+        self.rep["embed"] = (off, (V, d))
+        off += _round_up(V * d, 64)
+        self.rep_decay_end = off
+        for l in range(cfg.n_layers):
+            for nm in (f"l{l}.n1", f"l{l}.n2"):
+                self.rep[nm] = (off, (d,))
+                off += _round_up(d, 64)
+        self.rep["nf"] = (off, (d,))
+        off += _round_up(d, 64)
+        self.numel_rep = _round_up(off, 1024)
+        self.index = {**{n: None for n in self.mat}, **{n: None for n in self.rep}}
+
+        # ---- storage
+        self._symm = None
+        if f > 1:
+            from ..parallel.symm import SymmBuffer
+
+            self._symm = SymmBuffer(self.numel_shard * 2, fsdp_group, self.device)
+            self.p16_shard = self._symm.local.view(torch.bfloat16)[:self.numel_shard]
+            max_shard = max(_round_up(sr * Kd, 64) for (_, _, Kd, sr) in self.mat.values())
+            self._scratch = torch.empty((f - 1) * max_shard, device=self.device, dtype=torch.bfloat16)
+            self._max_shard = max_shard
+            self._flags = torch.zeros(8, dtype=torch.int32, device=self.device)
+            self._flag_base = 0
+        else:
+            self.p16_shard = torch.empty(self.numel_shard, device=self.device, dtype=torch.bfloat16)
+        self.p16_rep = torch.empty(self.numel_rep, device=self.device, dtype=torch.bfloat16)
+        self.g32: Optional[torch.Tensor] = None
+        self._init_weights(seed)
+        self.p32_s = self.m_s = self.v_s = self.p32_r = self.m_r = self.v_r = None
+        if with_optimizer:
+            self.p32_s = self.p16_shard.float()
+            self.m_s = torch.zeros_like(self.p32_s)
+            self.v_s = torch.zeros_like(self.p32_s)
+            self.p32_r = self.p16_rep.float()
+            self.m_r = torch.zeros_like(self.p32_r)
+            self.v_r = torch.zeros_like(self.p32_r)
+        if f > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=fsdp_group)
+
+    # ------------------------------------------------------------------ init
+    def _init_weights(self, seed: int) -> None:
+        """N(0, init_std) per tensor from a generator seeded by (seed, tensor index): the values do
+        not depend on the sharding."""
+        cfg = self.cfg
+        self.p16_shard.zero_()
+        self.p16_rep.zero_()
+        gen = torch.Generator(device=self.device)
+        for ti, (name, (off, N, Kd, sr)) in enumerate(self.mat.items()):
+            gen.manual_seed(seed * 100003 + ti)
+            r0 = self.shard_index * sr
+            r1 = min(N, r0 + sr)
+            full = torch.randn(N, Kd, device=self.device, generator=gen) * cfg.init_std
+            if r1 > r0:
+                self.p16_shard[off:off + (r1 - r0) * Kd].view(r1 - r0, Kd).copy_(full[r0:r1])
+            del full
+        gen.manual_seed(seed * 100003 + 99991)
+        eoff, eshape = self.rep["embed"]
+        self.p16_rep[eoff:eoff + math.prod(eshape)].view(eshape).copy_(
+            torch.randn(*eshape, device=self.device, generator=gen) * cfg.init_std)
+        for name, (off, shape) in self.rep.items():
+            if len(shape) == 1:
+                self.p16_rep[off:off + shape[0]] = 1.0
+
+    # ------------------------------------------------------------------ views
+    @property
+    def numel_grads(self) -> int:
+        return self.shard_count * self.numel_shard + self.numel_rep
+
+    def ensure_grads(self) -> torch.Tensor:
+        if self.g32 is None:
+            self.g32 = torch.zeros(self.numel_grads, device=self.device, dtype=torch.float32)
+        return self.g32
+
+    def grad_shard(self, s: int) -> torch.Tensor:
+        return self.g32[s * self.numel_shard:(s + 1) * self.numel_shard]
+
+    def grad_rep(self) -> torch.Tensor:
+        return self.g32[self.shard_count * self.numel_shard:]
+
+    def w(self, name: str) -> torch.Tensor:
+        """Replicated tensors always; matrices only when they are not sharded."""
+        if name in self.rep:
+            off, shape = self.rep[name]
+            return self.p16_rep[off:off + math.prod(shape)].view(shape)
+        off, N, Kd, sr = self.mat[name]
+        if self.shard_count != 1:
+            raise RuntimeError(f"{name} is sharded over {self.shard_count} ranks; use lin_fwd/lin_dgrad")
+        return self.p16_shard[off:off + N * Kd].view(N, Kd)
+
+    def w_shard(self, name: str) -> torch.Tensor:
+        """This rank's rows of a matrix (``(rows, K)``; the last shard may be shorter)."""
+        off, N, Kd, sr = self.mat[name]
+        rows = max(0, min(sr, N - self.shard_index * sr))
+        return self.p16_shard[off:off + rows * Kd].view(rows, Kd)
+
+    def g(self, name: str) -> torch.Tensor:
+        if name in self.rep:
+            off, shape = self.rep[name]
+            return self.grad_rep()[off:off + math.prod(shape)].view(shape)
+        off, N, Kd, sr = self.mat[name]
+        if self.shard_count != 1:
+            raise RuntimeError(f"{name} is sharded; its gradient is stored shard by shard")
+        return self.g32[off:off + N * Kd].view(N, Kd)
+
+    def g_full(self, name: str) -> torch.Tensor:
+        """Gradient of a matrix assembled to ``(N, K)`` (a copy when sharded; for tests)."""
+        if name in self.rep or self.shard_count == 1:
+            return self.g(name)
+        off, N, Kd, sr = self.mat[name]
+        parts = []
+        for s in range(self.shard_count):
+            rows = max(0, min(sr, N - s * sr))
+            parts.append(self.grad_shard(s)[off:off + rows * Kd].view(rows, Kd))
+        return torch.cat(parts, dim=0)
+
+    def n_params(self) -> int:
+        return sum(N * Kd for (_, N, Kd, _) in self.mat.values()) + sum(math.prod(s) for _, s in self.rep.values())
+
+    # ------------------------------------------------------------------ linear layers
+    def _gather_call(self, x, name, b_mn: int, out, residual, M, N, Kg):
+        off, Nw, Kw, sr = self.mat[name]
+        f, me = self.shard_count, self.shard_index
+        local_ptrs, src_ptrs = [], []
+        slot = 0
+        for s in range(f):
+            if s == me:
+                local_ptrs.append(self.p16_shard.data_ptr() + off * 2)
+                src_ptrs.append(0)
+            else:
+                local_ptrs.append(self._scratch.data_ptr() + slot * self._max_shard * 2)
+                src_ptrs.append(self._symm.peer_ptrs[s] + off * 2)
+                slot += 1
+        LP = (c_vp * f)(*local_ptrs)
+        SP = (c_vp * f)(*src_ptrs)
+        self._flag_base += self.gather_ctas
+        c_fp32 = 1 if out.dtype == torch.float32 else 0
+        _lib.call("ra_gemm_bf16_gather", c_vp(x.data_ptr()), c_vp(out.data_ptr()),
+                  c_vp(0 if residual is None else residual.data_ptr()), M, N, Kg,
+                  c_ll(x.stride(0)), c_ll(out.stride(0)), c_ll(0 if residual is None else residual.stride(0)),
+                  b_mn, c_fp32, f, me, sr, c_ll(Kw), LP, SP, c_vp(self._flags.data_ptr()),
+                  ctypes.c_uint(self._flag_base & 0xFFFFFFFF), self.gather_ctas, 8,
+                  c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr())
+        return out
+
+    def lin_fwd(self, x, name: str, out=None, residual=None):
+        """``y = x W^T (+ residual)``."""
+        off, N, Kd, sr = self.mat[name]
+        if self.shard_count == 1:
+            return K.linear_fwd(x, self.w(name), out=out, residual=residual)
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+        return self._gather_call(x, name, 0, out, residual, M, N, Kd)
+
+    def lin_dgrad(self, dy, name: str, out=None, residual=None):
+        """``dx = dy W (+ residual)``."""
+        off, N, Kd, sr = self.mat[name]
+        if self.shard_count == 1:
+            return K.linear_dgrad(dy, self.w(name), out=out, residual=residual)
+        M = dy.shape[0]
+        if out is None:
+            out = torch.empty(M, Kd, device=dy.device, dtype=torch.bfloat16)
+        return self._gather_call(dy, name, 1, out, residual, M, Kd, N)
+
+    def lin_wgrad(self, dy, x, name: str) -> None:
+        """``dW += dy^T x`` (fp32). With sharding, each shard's rows are a GEMM of their own, written
+        into that shard's segment of the gradient buffer."""
+        off, N, Kd, sr = self.mat[name]
+        if self.shard_count == 1:
+            K.linear_wgrad(dy, x, self.g(name))
+            return
+        for s in range(self.shard_count):
+            r0 = s * sr
+            rows = max(0, min(sr, N - r0))
+            if rows == 0:
+                continue
+            acc = self.grad_shard(s)[off:off + rows * Kd].view(rows, Kd)
+            K.gemm(dy[:, r0:r0 + rows], x, a_mn=True, b_mn=True, out=acc, residual=acc)
+
+    # ------------------------------------------------------------------ optimizer
+    def adamw_step(self, step: int, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+                   clip: float, gnorm_sq) -> None:
+        common = dict(step=step, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
+                      clip=clip, gnorm_sq=gnorm_sq)
+        K.adamw_(self.p32_s, self.m_s, self.v_s, self.grad_shard(self.shard_index), self.p16_shard,
+                 decay_end=self.numel_shard, **common)
+        K.adamw_(self.p32_r, self.m_r, self.v_r, self.grad_rep(), self.p16_rep,
+                 decay_end=self.rep_decay_end, **common)
+
+    def state_dict(self) -> dict:
+        return {"p32_s": self.p32_s.cpu(), "m_s": self.m_s.cpu(), "v_s": self.v_s.cpu(),
+                "p32_r": self.p32_r.cpu(), "m_r": self.m_r.cpu(), "v_r": self.v_r.cpu(),
+                "shard": (self.shard_index, self.shard_count)}
+
+    def load_state_dict(self, st: dict) -> None:
+        if tuple(st["shard"]) != (self.shard_index, self.shard_count):
+            raise ValueError("checkpoint was written with a different fsdp sharding")
+        for k in ("p32_s", "m_s", "v_s", "p32_r", "m_r", "v_r"):
+            getattr(self, k).copy_(st[k])
+        self.p16_shard.copy_(self.p32_s)
+        self.p16_rep.copy_(self.p32_r)

@@ -86,9 +86,11 @@ class DeviceMesh:
 
     AXES = MeshConfig.AXES
 
-    def __init__(self, config: "MeshConfig | str", register: bool = True):
+    def __init__(self, config: "MeshConfig | str", register: bool = True, standalone: bool = False):
+        """``standalone=True`` builds a one-rank mesh even inside a multi-process job (a replica that
+        takes no part in any collective; used for single-device reference runs)."""
         self.config = MeshConfig.parse(config)
-        if dist.is_available() and dist.is_initialized():
+        if not standalone and dist.is_available() and dist.is_initialized():
             self.world_size = dist.get_world_size()
             self.rank = dist.get_rank()
         else:

@@ -14,7 +14,8 @@ import torch
 import torch.distributed as dist
 
 from .config import LlamaConfig, MeshConfig, TrainConfig
-from .models.llama import FlatParams, LlamaModel, StepContext
+from .models.llama import LlamaModel, StepContext
+from .models.params import FlatParams
 from .ops import _lib
 from .ops import kernels as K
 from .ops.reference import shard_positions
@@ -73,17 +74,21 @@ class Trainer:
     """Owns the model replica of this rank and runs training steps on the mesh.
 
     Mesh semantics: ``sp`` shards the sequence (ring attention), ``dp`` and ``fsdp`` shard the
-    batch; parameters are replicated over ``sp``/``dp``; over ``fsdp`` the optimizer state is
-    sharded (each rank updates its slice and the updated bf16 weights are all-gathered).
+    batch; parameters are replicated over ``sp``/``dp``; over ``fsdp`` every GEMM weight, its fp32
+    master copy and its AdamW moments are row-sharded, and the shards of the other ranks are pulled
+    inside the GEMM that needs them (see ``models/params.py``).
     """
 
     def __init__(self, model_cfg: LlamaConfig, train_cfg: TrainConfig, mesh: Optional[DeviceMesh] = None,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, standalone: bool = False):
         self.cfg = model_cfg
         self.tc = train_cfg
         self.rank, self.world, self.local_rank = init_distributed()
+        if standalone:  # a one-rank replica inside a larger job: joins no collective
+            self.rank, self.world = 0, 1
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.mesh = mesh or DeviceMesh(MeshConfig.parse(train_cfg.mesh))
+        self.mesh = mesh or DeviceMesh(MeshConfig.parse(train_cfg.mesh), register=not standalone,
+                                       standalone=standalone)
         self.sp_rank, self.sp = self.mesh.index("sp"), self.mesh.size("sp")
         self.fsdp_rank, self.fsdp = self.mesh.index("fsdp"), self.mesh.size("fsdp")
         self.dp_rank, self.dp = self.mesh.index("dp"), self.mesh.size("dp")
@@ -96,7 +101,8 @@ class Trainer:
         self.B = train_cfg.global_batch // self.batch_groups
         self.S = train_cfg.seq_len // self.sp
         params = FlatParams(model_cfg, self.device, seed=train_cfg.seed, with_optimizer=True,
-                            shard=(self.fsdp_rank, self.fsdp))
+                            shard=(self.fsdp_rank, self.fsdp),
+                            fsdp_group=self.mesh.axis("fsdp").group if self.fsdp > 1 else None)
         self.model = LlamaModel(model_cfg, self.device, params=params)
         self.symm_ring = None
         if self.sp > 1:
@@ -105,6 +111,7 @@ class Trainer:
             self.symm_ring = SymmRing(self.mesh.axis("sp").group, self.device)
             self.mesh.axis("sp").symm_ring = self.symm_ring
         self.step_idx = 0
+        self._sync_token = torch.zeros(1, device=self.device)
         self.gnorm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
         self.gen = torch.Generator()
         self.gen.manual_seed(train_cfg.seed + 1)
@@ -168,18 +175,15 @@ class Trainer:
     def optimizer_step(self) -> None:
         P, tc = self.model.params, self.tc
         self.step_idx += 1
-        lo, hi = P.shard_range()
         clip = float(tc.grad_clip)
         if clip > 0:
             self.gnorm_sq.zero_()
             K.sumsq(P.g32, self.gnorm_sq)
-        decay_end = max(0, min(P.decay_end, hi) - lo)
-        K.adamw_(P.p32, P.m, P.v, P.g32[lo:hi], P.p16[lo:hi], step=self.step_idx, lr=tc.lr,
-                 beta1=tc.beta1, beta2=tc.beta2, eps=tc.eps, weight_decay=tc.weight_decay,
-                 decay_end=decay_end, clip=clip, gnorm_sq=self.gnorm_sq if clip > 0 else None)
+        P.adamw_step(self.step_idx, tc.lr, tc.beta1, tc.beta2, tc.eps, tc.weight_decay, clip,
+                     self.gnorm_sq if clip > 0 else None)
         if self.fsdp > 1:
-            group = self.mesh.axis("fsdp").group
-            dist.all_gather_into_tensor(P.p16, P.p16[lo:hi].clone(), group=group)
+            # peers pull this rank's shard inside their GEMMs: order the update before their next step
+            dist.all_reduce(self._sync_token, group=self.mesh.axis("fsdp").group)
 
     # ------------------------------------------------------------------ failure detection (host side)
     def _store(self):
@@ -231,8 +235,9 @@ class Trainer:
         os.makedirs(directory, exist_ok=True)
         P = self.model.params
         path = os.path.join(directory, f"rank{self.rank}.pt")
-        torch.save({"p32": P.p32.cpu(), "m": P.m.cpu(), "v": P.v.cpu(), "step": self.step_idx,
-                    "gen": self.gen.get_state(), "shard": (P.shard_index, P.shard_count)}, path)
+        st = P.state_dict()
+        st.update(step=self.step_idx, gen=self.gen.get_state())
+        torch.save(st, path)
         if self.rank == 0:
             with open(os.path.join(directory, "meta.json"), "w") as f:
                 json.dump({"step": self.step_idx, "world": self.world, "mesh": self.mesh.config.shape(),
@@ -242,16 +247,10 @@ class Trainer:
         return path
 
     def load_checkpoint(self, directory: str) -> None:
-        P = self.model.params
         st = torch.load(os.path.join(directory, f"rank{self.rank}.pt"), map_location="cpu")
-        if tuple(st["shard"]) != (P.shard_index, P.shard_count):
-            raise ValueError("checkpoint was written with a different fsdp sharding")
-        P.p32.copy_(st["p32"])
-        P.m.copy_(st["m"])
-        P.v.copy_(st["v"])
+        self.model.params.load_state_dict(st)
         self.step_idx = int(st["step"])
         self.gen.set_state(st["gen"])
-        lo, hi = P.shard_range()
-        P.p16[lo:hi].copy_(P.p32)
-        if self.fsdp > 1:
-            dist.all_gather_into_tensor(P.p16, P.p16[lo:hi].clone(), group=self.mesh.axis("fsdp").group)
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()

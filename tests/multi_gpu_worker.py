@@ -120,6 +120,47 @@ def decode_and_inference(rank, world, dev):
     return ok
 
 
+def fsdp_parity(rank, world, dev):
+    """fsdp = world: weights row-sharded, remote shards gathered inside the GEMMs. The loss of the
+    sharded run must equal a replicated single-device run on the same global batch, step after step."""
+    from ringattention_b200.models.llama import LlamaModel
+    from ringattention_b200.parallel.mesh import DeviceMesh
+
+    ok = True
+    cfg = LlamaConfig.named("llama-tiny")
+    tc = TrainConfig(model="llama-tiny", mesh=f"1,{world},1,1", seq_len=512, global_batch=world, lr=1e-3, seed=21)
+    tr = Trainer(cfg, tc, mesh=DeviceMesh(f"1,{world},1,1", register=False))
+    tokens, targets, seg = tr.make_global_batch()
+    # gather GEMMs against the assembled matrix
+    P = tr.model.params
+    name = "l0.wqkv"
+    parts = [torch.zeros(P.mat[name][3], P.mat[name][2], device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    mine = torch.zeros_like(parts[0])
+    ws = P.w_shard(name)
+    mine[:ws.shape[0]] = ws
+    dist.all_gather(parts, mine, group=tr.mesh.axis("fsdp").group)
+    W = torch.cat(parts, 0)[:P.mat[name][1]]
+    x = torch.randn(300, W.shape[1], device=dev).bfloat16()
+    dy = torch.randn(300, W.shape[0], device=dev).bfloat16()
+    y = P.lin_fwd(x, name)
+    dx = P.lin_dgrad(dy, name)
+    e1 = ((y.float() - x.float() @ W.float().t()).abs().max() / (x.float() @ W.float().t()).abs().max()).item()
+    e2 = ((dx.float() - dy.float() @ W.float()).abs().max() / (dy.float() @ W.float()).abs().max()).item()
+    ok &= e1 < 0.02 and e2 < 0.02
+    print(f"[{rank}] gather GEMM fwd rel err {e1:.4f} dgrad rel err {e2:.4f}", flush=True)
+    losses = [tr.train_step(tokens, targets, seg) for _ in range(3)]
+    # replicated reference on one device (every rank computes it; only losses are compared)
+    ref_tc = TrainConfig(model="llama-tiny", mesh="1,1,1,1", seq_len=512, global_batch=world, lr=1e-3, seed=21)
+    ref = Trainer(cfg, ref_tc, standalone=True)
+    ref_losses = [ref.train_step(tokens, targets, seg) for _ in range(3)]
+    d = max(abs(a - b) for a, b in zip(losses, ref_losses))
+    ok &= d < 3e-2 and losses[-1] < losses[0]
+    print(f"[{rank}] fsdp losses {[round(v, 4) for v in losses]} vs replicated {[round(v, 4) for v in ref_losses]}", flush=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return ok
+
+
 def main():
     rank, world, local = init_distributed()
     dev = torch.device("cuda", local)
@@ -128,6 +169,7 @@ def main():
     DeviceMesh(f"1,1,1,{world}")
     ok = ring_vs_dense(rank, world, dev)
     ok &= decode_and_inference(rank, world, dev)
+    ok &= fsdp_parity(rank, world, dev)
     ok2, left = trainer_parity_and_peer_loss(rank, world, dev)
     print(f"[{rank}] RESULT {'OK' if (ok and ok2) else 'FAIL'}", flush=True)
     os._exit(0 if (ok and ok2) else 1)
