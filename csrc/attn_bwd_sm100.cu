@@ -26,6 +26,13 @@ namespace ra {
 namespace attn {
 
 constexpr int BWD_THREADS = 512;
+// Register re-balancing: the CTA owns 512 x 128 registers (launch bounds); setmaxnreg.inc blocks
+// until registers are free, so the per-group budgets must fit in that allocation.
+constexpr int BWD_REGS_PRODUCER = 80;  // warps 0-3
+constexpr int BWD_REGS_SOFTMAX = 144;  // warps 4-11
+constexpr int BWD_REGS_DRAIN = 144;    // warps 12-15
+static_assert(128 * BWD_REGS_PRODUCER + 256 * BWD_REGS_SOFTMAX + 128 * BWD_REGS_DRAIN <= BWD_THREADS * 128,
+              "setmaxnreg budgets exceed the registers the CTA was launched with");
 
 struct BwdParams {
   int B, H;
@@ -197,7 +204,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
   if (warp < 4) {
     // ================================================================ producer warpgroup
-    setmaxnreg_dec<80>();
+    setmaxnreg_dec<BWD_REGS_PRODUCER>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       mbar_arrive_expect_tx(kv_full, 2 * SM::TILE_BYTES);
@@ -227,8 +234,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tma_load_4d(sDO + s * SM::SLAB_BYTES, &tma_do, do_full, s * 64, h, qi0, b);
         ++it;
       }
-    } else if (warp == 1 && lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 1) {
+      // ---------------------------------------------------------------- MMA issuer (warp-uniform flow)
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, 0, 1);
       constexpr uint32_t idesc_dk = make_idesc_bf16(128, D, 0, 1);
@@ -251,9 +259,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
-          umma_ss(tS, desc_advance(k_k, off), desc_advance(q_k[st], off), idesc_s, kk != 0 ? 1u : 0u);
+          if (leader)
+            umma_ss(tS, desc_advance(k_k, off), desc_advance(q_k[st], off), idesc_s, kk != 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
+        if (leader) umma_commit(s_full);
       };
       auto next_visible = [&](int i) {
         for (; i < nqt; ++i)
@@ -277,23 +286,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (!mbar_wait(do_full, par, wc, kTimeoutSmemFull)) break;
         if (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, wc, kTimeoutTmemEmpty)) break;
         tc_fence_after();
-        trace_event(p.trace, tr, 0, it, 0);
+        trace_event(p.trace, tr && leader, 0, it, 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
-          umma_ss(tDP, desc_advance(v_k, off), desc_advance(do_k, off), idesc_s, kk != 0 ? 1u : 0u);
+          if (leader)
+            umma_ss(tDP, desc_advance(v_k, off), desc_advance(do_k, off), idesc_s, kk != 0 ? 1u : 0u);
         }
-        umma_commit(dp_full);
+        if (leader) umma_commit(dp_full);
         // dV += P^T dO
         if (!mbar_wait(p_ready, par, wc, kTimeoutTmemFull)) break;
         tc_fence_after();
-        trace_event(p.trace, tr, 0, it, 1);
+        trace_event(p.trace, tr && leader, 0, it, 1);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_col = tS + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-          umma_ts(tDV, a_col, desc_advance(do_mn, kk * 2048), idesc_dv, (it != 0 || kk != 0) ? 1u : 0u);
+          if (leader)
+            umma_ts(tDV, a_col, desc_advance(do_mn, kk * 2048), idesc_dv, (it != 0 || kk != 0) ? 1u : 0u);
         }
-        umma_commit(do_empty);
+        if (leader) umma_commit(do_empty);
         // next S^T right away (P^T was consumed by the dV MMAs just issued), so that the softmax
         // group can work on it while dK/dQ of this iteration run
         const int in = next_visible(i + 1);
@@ -306,29 +317,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         // dK += dS^T Q ; dQ_i = dS K
         if (!mbar_wait(ds_ready, par, wc, kTimeoutTmemFull)) break;
         tc_fence_after();
-        trace_event(p.trace, tr, 0, it, 2);
+        trace_event(p.trace, tr && leader, 0, it, 2);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;
-          umma_ss(tDK, desc_advance(ds_k, a_off), desc_advance(q_mn[st], kk * 2048), idesc_dk,
-                  (it != 0 || kk != 0) ? 1u : 0u);
+          if (leader)
+            umma_ss(tDK, desc_advance(ds_k, a_off), desc_advance(q_mn[st], kk * 2048), idesc_dk,
+                    (it != 0 || kk != 0) ? 1u : 0u);
         }
-        umma_commit(&q_empty[st]);
+        if (leader) umma_commit(&q_empty[st]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tDP, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), idesc_dq,
-                  kk != 0 ? 1u : 0u);
-        umma_commit(dq_full);
-        trace_event(p.trace, tr, 0, it, 3);
+          if (leader)
+            umma_ss(tDP, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), idesc_dq,
+                    kk != 0 ? 1u : 0u);
+        if (leader) umma_commit(dq_full);
+        trace_event(p.trace, tr && leader, 0, it, 3);
         i = in;
         ++it;
       }
-      umma_commit(acc_full);
+      if (leader) umma_commit(acc_full);
     }
     __syncwarp();
   } else if (warp < 12) {
     // ================================================================ softmax / dS group
-    setmaxnreg_inc<144>();
+    setmaxnreg_inc<BWD_REGS_SOFTMAX>();
     const int quad = warp & 3;
     const int half = (warp - 4) >> 2;  // which 64 q-columns
     const int sm_tid = (warp - 4) * 32 + lane;
@@ -519,7 +532,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
   } else {
     // ================================================================ dQ drain group
-    setmaxnreg_inc<144>();
+    setmaxnreg_inc<BWD_REGS_DRAIN>();
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // q row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;

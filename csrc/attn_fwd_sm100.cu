@@ -21,6 +21,12 @@ namespace attn {
 
 constexpr int FWD_THREADS = 384;
 constexpr int KV_STAGES = 2;
+// Register re-balancing: the CTA owns 384 x 168 registers (launch bounds); setmaxnreg.inc blocks
+// until registers are free, so the per-group budgets must fit in that allocation.
+constexpr int FWD_REGS_PRODUCER = 88;   // warps 0-3
+constexpr int FWD_REGS_SOFTMAX = 208;   // warps 4-11
+static_assert(128 * FWD_REGS_PRODUCER + 256 * FWD_REGS_SOFTMAX <= FWD_THREADS * 168,
+              "setmaxnreg budgets exceed the registers the CTA was launched with");
 
 struct FwdParams {
   int B, H;
@@ -148,7 +154,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   const uint32_t tS[2] = {tmem_base, tmem_base + 128};
   const uint32_t tO[2] = {tmem_base + 256, tmem_base + 384};
 
-  if (warp < 4) setmaxnreg_dec<72>();
+  if (warp < 4) setmaxnreg_dec<FWD_REGS_PRODUCER>();
   if (warp == 0) {
     // ================================================================ TMA producer
     if (lane == 0) {
@@ -182,8 +188,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ================================================================ MMA issuer
-    if (lane == 0) {
+    // ================================================================ MMA issuer (warp-uniform flow)
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
       const uint64_t q_desc[2] = {make_smem_desc(smem_u32(sQ), 16, 1024),
@@ -196,19 +203,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * SM::SLAB_BYTES + (kk & 3) * 32;
-          umma_ss(tS[w], desc_advance(q_desc[w], off), desc_advance(k_desc[st], off), idesc_s,
-                  kk != 0 ? 1u : 0u);
+          if (leader)
+            umma_ss(tS[w], desc_advance(q_desc[w], off), desc_advance(k_desc[st], off), idesc_s,
+                    kk != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[w]);
+        if (leader) umma_commit(&s_full[w]);
       };
       auto issue_pv = [&](int w, int st, bool acc) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // A = P_w in TMEM: 16 bf16 of K per step = 8 columns. B = V, MN-major: 16 kv rows = 2 KiB.
-          umma_ts(tO[w], tS[w] + kk * 8, desc_advance(v_desc[st], kk * 2048), idesc_o,
-                  (acc || kk != 0) ? 1u : 0u);
+          if (leader)
+            umma_ts(tO[w], tS[w] + kk * 8, desc_advance(v_desc[st], kk * 2048), idesc_o,
+                    (acc || kk != 0) ? 1u : 0u);
         }
-        umma_commit(&o_done[w]);
+        if (leader) umma_commit(&o_done[w]);
       };
       auto next_visible = [&](int j, bool& v0, bool& v1) {
         for (; j < nk; ++j) {
@@ -230,7 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tc_fence_after();
           if (v0) issue_s(0, 0);
           if (v1) issue_s(1, 0);
-          umma_commit(&k_empty[0]);
+          if (leader) umma_commit(&k_empty[0]);
         }
       }
       while (ok && j < nk) {
@@ -260,14 +269,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           issue_pv(1, st, cnt[1] != 0);
           ++cnt[1];
         }
-        umma_commit(&v_empty[st]);
+        if (leader) umma_commit(&v_empty[st]);
         if (jn < nk) {
           if (n1) {
             if (!k_ready && !mbar_wait(&k_full[stn], phn, wc, kTimeoutSmemFull)) break;
             tc_fence_after();
             issue_s(1, stn);
           }
-          umma_commit(&k_empty[stn]);
+          if (leader) umma_commit(&k_empty[stn]);
         }
         j = jn;
         v0 = n0;
@@ -278,7 +287,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     __syncwarp();
   } else if (warp >= 4) {
     // ================================================================ softmax groups
-    setmaxnreg_inc<216>();
+    setmaxnreg_inc<FWD_REGS_SOFTMAX>();
     const int w = (warp - 4) >> 2;  // q tile handled by this group
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
@@ -325,10 +334,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       float sc = p.scale_log2;  // multiplier still to be applied to sr[] inside the exp
       float mx = -INFINITY;
       if (plain) {
-        mx = fmaxf(__uint_as_float(sr[0]), __uint_as_float(sr[1]));
+        float mc[4];
 #pragma unroll
-        for (int i = 2; i < 128; i += 2) mx = max3(mx, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-        mx *= sc;
+        for (int c = 0; c < 4; ++c) mc[c] = fmaxf(__uint_as_float(sr[32 * c]), __uint_as_float(sr[32 * c + 1]));
+#pragma unroll
+        for (int i = 2; i < 32; i += 2) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            mc[c] = max3(mc[c], __uint_as_float(sr[32 * c + i]), __uint_as_float(sr[32 * c + i + 1]));
+        }
+        mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3])) * sc;
       } else {
         const int limit = causal_col_limit(mk, qpos, k0);
         const int* segb = sSeg + (w * 2 + (cnt & 1)) * 128;

@@ -75,6 +75,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase (no suspension); used by issuers that serve several
+// independent pipelines and must never block on one of them.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Per-CTA context for bounded waits.
 struct WaitCtx {
   volatile int* abort_smem;  // CTA-wide abort flag (shared memory)
@@ -245,6 +261,21 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
          | (static_cast<uint32_t>(a_mn_major) << 15) // A major
          | (static_cast<uint32_t>(b_mn_major) << 16) // B major
          | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// One lane of a fully active warp (the same lane every time). Issuing warps keep their control
+// flow and descriptor arithmetic warp-uniform and predicate only the tcgen05 instruction itself,
+// which lets the compiler keep descriptors in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.

@@ -221,8 +221,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (warp-uniform flow)
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
@@ -249,16 +250,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                         : make_smem_desc(a_addr + kk * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + kk * 2048, SLAB_BYTES, 1024)
                                         : make_smem_desc(b_addr + kk * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (leader) umma_ss(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty[stage]);
+          if (leader) umma_commit(&empty[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(&tfull[acc]);
+        if (leader) umma_commit(&tfull[acc]);
         if (++acc == NUM_ACC) {
           acc = 0;
           acc_phase ^= 1u;
