@@ -99,6 +99,7 @@ class SymmRing:
         self.timeout_ns = int(float(os.environ.get("RINGATTN_B200_BARRIER_TIMEOUT_S",
                                                    timeout_s if timeout_s is not None else 120.0)) * 1e9)
         self.copy_ctas = copy_ctas
+        self.overlap = True  # False: pull each block with a separate copy kernel before its step (for measurements)
         self.epoch = 0
         self.calls = 0
         self._bufs: Dict[str, SymmBuffer] = {}
@@ -160,6 +161,15 @@ class SymmRing:
         t = slabs[i * nb:(i + 1) * nb].view(torch.bfloat16).view(B, S, 2, H, D)
         return t[:, :, 0], t[:, :, 1]
 
+    def _maybe_serial_copy(self, cp: dict) -> dict:
+        """With ``overlap`` off, do the pull with a stand-alone copy kernel now (stream order puts it
+        before the step that would have carried it) and hand the attention kernel no copy job."""
+        if self.overlap:
+            return cp
+        _lib.call("ra_peer_copy", c_vp(cp["copy_src"]), c_vp(cp["copy_dst"]), ctypes.c_longlong(cp["copy_bytes"]),
+                  64, _lib.stream_ptr())
+        return {}
+
     # ------------------------------------------------------------------ fused forward
     def forward(self, q, k, v, plan, out=None):
         B, Sq, H, D = q.shape
@@ -188,6 +198,7 @@ class SymmRing:
             if i + 1 < n and steps[i + 1].block != self.rank:
                 cp = dict(copy_src=own.peer_ptrs[steps[i + 1].block] + slot * nb,
                           copy_dst=slabs.data_ptr() + (i & 1) * nb, copy_bytes=nb, copy_ctas=self.copy_ctas)
+                cp = self._maybe_serial_copy(cp)
             last = i == n - 1
             flash.flash_fwd(q, kk, vv, st.mask, o_prev=o_acc if have_prev else None,
                             lse_prev=lse if have_prev else None, out=out if last else o_acc,
@@ -217,6 +228,7 @@ class SymmRing:
             if i + 1 < n and steps[i + 1].block != self.rank:
                 cp = dict(copy_src=own.peer_ptrs[steps[i + 1].block] + slot * nb,
                           copy_dst=slabs.data_ptr() + (i & 1) * nb, copy_bytes=nb, copy_ctas=self.copy_ctas)
+                cp = self._maybe_serial_copy(cp)
             flash.flash_bwd(q, kk, vv, dout, lse2, delta, st.mask, dq_acc, t5[:, :, 0], t5[:, :, 1],
                             flash.DKV_REDUCE_FP32, **cp)
         self.barrier()
