@@ -112,6 +112,44 @@ class BlockwiseKwargs:
         return int(rng) & (2**63 - 1)
 
 
+@dataclass(frozen=True)
+class SegmentIds:
+    """Per-token segment ids of the queries and of the keys/values of one attention call (the
+    reference's ``SegmentIds`` NamedTuple, ringattention_pallas_tpu.py:201-215). Tokens attend only
+    to tokens with an equal id."""
+
+    q: Any
+    kv: Any
+
+
+@dataclass(frozen=True)
+class BlockSizes:
+    """Tile sizes of the fused kernels. The reference exposes eleven tunable TPU tile sizes
+    (ringattention_pallas_tpu.py:218-287, default 128 everywhere); the sm_100a kernels are built for
+    one tile shape, fixed by the tcgen05 instruction shape and the TMEM budget, so this object is
+    informational: ``validate`` only checks that a request is compatible."""
+
+    block_q: int = 256          # query rows per CTA in the forward (two 128-row tiles)
+    block_k: int = 128          # key rows per pipeline step
+    block_q_bwd: int = 128      # query rows per backward iteration
+    block_k_bwd: int = 128      # key rows per backward CTA
+    block_b: int = 1
+
+    @classmethod
+    def get_default(cls) -> "BlockSizes":
+        return cls()
+
+    def validate(self, q_len: int, kv_len: int) -> None:
+        if self.block_b != 1:
+            raise ValueError("block_b must be 1")
+        for name in ("block_q", "block_k", "block_q_bwd", "block_k_bwd"):
+            v = getattr(self, name)
+            if v % 128:
+                raise ValueError(f"{name} must be a multiple of 128")
+        if q_len < 1 or kv_len < 1:
+            raise ValueError("empty sequence")
+
+
 @dataclass
 class MeshConfig:
     """Sizes of the four mesh axes used in the reference's README (README.md:38-46)."""

@@ -1,0 +1,155 @@
+"""Host-side model of the symmetric-memory protocol used by the fused ring (a race detector that
+needs no GPU).
+
+The kernels of one rank run in stream order; different ranks run concurrently and only meet at the
+flag barrier. A schedule is safe if no rank ever writes a buffer while another rank may still be
+reading or writing it. :func:`check_schedule` explores *every* interleaving of N ranks that the
+barriers allow (each kernel is a begin and an end event with read and write sets) and reports the
+first conflict. The programs below mirror ``parallel/symm.py`` and ``ops/decode.py``; the tests run
+them for small N and several consecutive calls, and also check that removing a barrier or the
+double buffering is detected.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, FrozenSet, List, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class Op:
+    kind: str                       # "kernel" or "barrier"
+    reads: FrozenSet[Tuple] = frozenset()
+    writes: FrozenSet[Tuple] = frozenset()
+    name: str = ""
+
+
+def kernel(name, reads=(), writes=()) -> Op:
+    return Op("kernel", frozenset(reads), frozenset(writes), name)
+
+
+BARRIER = Op("barrier", name="barrier")
+
+
+def ring_forward_program(rank: int, n: int, calls: int, double_buffer: bool = True, barrier: bool = True) -> List[Op]:
+    """Forward of ``SymmRing``: stage own KV into slot (call & 1), barrier, then N steps; the kernel
+    of step i reads slab (i-1)&1 and pulls block (rank-i-1) from its owner into slab i&1."""
+    ops: List[Op] = []
+    for c in range(calls):
+        slot = (c & 1) if double_buffer else 0
+        ops.append(kernel(f"stage{c}", writes=[("own", rank, slot)]))
+        if barrier:
+            ops.append(BARRIER)
+        for i in range(n):
+            reads, writes = [], []
+            if i > 0:
+                reads.append(("slab", rank, (i - 1) & 1))
+            if i + 1 < n:
+                src = (rank - i - 1) % n
+                reads.append(("own", src, slot))
+                writes.append(("slab", rank, i & 1))
+            ops.append(kernel(f"step{c}.{i}", reads, writes))
+    return ops
+
+
+def ring_backward_program(rank: int, n: int, calls: int, second_barrier: bool = True) -> List[Op]:
+    """Backward: zero own accumulator, stage KV, barrier, steps that reduce into the owner's
+    accumulator, barrier, cast own accumulator."""
+    ops: List[Op] = []
+    for c in range(calls):
+        slot = c & 1
+        ops.append(kernel(f"zero{c}", writes=[("acc", rank)]))
+        ops.append(kernel(f"stage{c}", writes=[("own", rank, slot)]))
+        ops.append(BARRIER)
+        for i in range(n):
+            blk = (rank - i) % n
+            reads, writes = [], [("acc+", blk)]  # reductions commute: tracked as a separate class
+            if i > 0:
+                reads.append(("slab", rank, (i - 1) & 1))
+            if i + 1 < n:
+                reads.append(("own", (rank - i - 1) % n, slot))
+                writes.append(("slab", rank, i & 1))
+            ops.append(kernel(f"bstep{c}.{i}", reads, writes))
+        if second_barrier:
+            ops.append(BARRIER)
+        ops.append(kernel(f"cast{c}", reads=[("acc", rank)]))
+    return ops
+
+
+def decode_program(rank: int, n: int, calls: int, double_buffer: bool = True) -> List[Op]:
+    """Decode merge: store the partial into slot `rank` of every inbox, barrier, merge own inbox."""
+    ops: List[Op] = []
+    for c in range(calls):
+        slot = (c & 1) if double_buffer else 0
+        ops.append(kernel(f"push{c}", writes=[("inbox", r, slot, rank) for r in range(n)]))
+        ops.append(BARRIER)
+        ops.append(kernel(f"merge{c}", reads=[("inbox", rank, slot, s) for s in range(n)]))
+    return ops
+
+
+def _conflict(a_reads, a_writes, b_reads, b_writes) -> Optional[Tuple]:
+    def base(x):  # ("acc+", r) and ("acc", r) name the same memory
+        return ("acc",) + x[1:] if x[0] == "acc+" else x
+
+    for w in a_writes:
+        for other in list(b_reads) + list(b_writes):
+            if base(w) == base(other):
+                if w[0] == "acc+" and other[0] == "acc+":
+                    continue  # concurrent reductions into the same accumulator are fine
+                return w
+    for r in a_reads:
+        for w in b_writes:
+            if base(r) == base(w):
+                return r
+    return None
+
+
+def check_schedule(programs: List[List[Op]]) -> Optional[str]:
+    """Explore all interleavings; return a description of the first race found, or ``None``."""
+    n = len(programs)
+    # state: per rank (pc, running) where running means the kernel at pc has begun but not ended
+    start = tuple((0, False) for _ in range(n))
+    seen = {start}
+    stack = [start]
+    while stack:
+        st = stack.pop()
+        for r in range(n):
+            pc, running = st[r]
+            if pc >= len(programs[r]):
+                continue
+            op = programs[r][pc]
+            if op.kind == "barrier":
+                # passes only when every rank has reached its matching barrier (same ordinal)
+                k = sum(1 for o in programs[r][:pc] if o.kind == "barrier")
+                ok = True
+                for s in range(n):
+                    spc, srun = st[s]
+                    arrived = sum(1 for o in programs[s][:spc] if o.kind == "barrier")
+                    at_barrier = spc < len(programs[s]) and programs[s][spc].kind == "barrier" and not srun
+                    if not (arrived > k or (arrived == k and at_barrier)):
+                        ok = False
+                        break
+                if not ok:
+                    continue
+                nxt = list(st)
+                nxt[r] = (pc + 1, False)
+            elif not running:
+                # begin: conflicts with kernels running on other ranks?
+                for s in range(n):
+                    if s == r:
+                        continue
+                    spc, srun = st[s]
+                    if srun:
+                        o2 = programs[s][spc]
+                        c = _conflict(op.reads, op.writes, o2.reads, o2.writes)
+                        if c is not None:
+                            return f"rank {r} {op.name} races with rank {s} {o2.name} on {c}"
+                nxt = list(st)
+                nxt[r] = (pc, True)
+            else:
+                nxt = list(st)
+                nxt[r] = (pc + 1, False)
+            t = tuple(nxt)
+            if t not in seen:
+                seen.add(t)
+                stack.append(t)
+    return None

@@ -1,0 +1,73 @@
+"""Per-GPU memory model of a training step and the maximum trainable context it implies.
+
+    python -m ringattention_b200.utils.memory --model llama-7b --gpus 1 2 4 8
+
+The model mirrors what the driver allocates (``models/params.py``, ``models/llama.py``,
+``parallel/symm.py``): bf16 weights, fp32 master + two AdamW moments (sharded over fsdp), fp32
+gradients (full size), one saved layer input per layer (``nothing_saveable``), the working set of one
+layer being recomputed and differentiated, the chunked FFN / LM-head temporaries and, for sp > 1,
+the symmetric KV slots, the two local slabs, the fp32 dK/dV accumulator and the fp32 output carry.
+Activation memory is linear in the tokens per GPU, so the maximum context grows linearly with the
+number of GPUs on the sp axis (the reference's claim, README.md:5).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+from ..config import LlamaConfig
+
+GiB = 1024 ** 3
+
+
+def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int = 1, batch: int = 1) -> dict:
+    n_mat = cfg.n_layers * (4 * cfg.d_model ** 2 + 3 * cfg.d_model * cfg.d_ff) + cfg.vocab_size * cfg.d_model
+    n_rep = cfg.vocab_size * cfg.d_model + (2 * cfg.n_layers + 1) * cfg.d_model
+    T = tokens_per_gpu * batch
+    d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+    weights = (n_mat / fsdp + n_rep) * 2 + (0 if fsdp == 1 else (fsdp - 1) / fsdp * 2 * max(3 * d * d, 2 * F * d, V * d))
+    optimizer = (n_mat / fsdp + n_rep) * 12
+    grads = (n_mat + n_rep) * 4
+    saved = cfg.n_layers * T * d * 2
+    # one layer in flight (recompute + backward): x2, h1, h2, qkv, attn, dqkv, dattn/dh buffers, dq fp32, lse/delta
+    layer = T * d * 2 * (1 + 1 + 1 + 3 + 1 + 3 + 2) + T * d * 4 + 3 * T * cfg.n_heads * 4
+    chunks = min(cfg.ffn_chunk_size, T) * (2 * F * 2 + 2 * F * 2) + min(cfg.loss_chunk_size, T) * V * 2
+    ring = 0
+    if sp > 1:
+        kv = T * 2 * d * 2
+        ring = 2 * kv + 2 * kv + T * 2 * d * 4 + T * d * 4
+    total = weights + optimizer + grads + saved + layer + chunks + ring
+    return {"weights": weights, "optimizer": optimizer, "grads": grads, "saved_layer_inputs": saved,
+            "layer_working_set": layer, "chunk_temporaries": chunks, "ring_buffers": ring, "total": total}
+
+
+def max_context(cfg: LlamaConfig, gpus: int, hbm_bytes: float = 178 * GiB, fsdp: int = 1, reserve: float = 0.06) -> int:
+    """Largest global sequence (multiple of 1024 tokens per GPU) that fits with sp = gpus / fsdp."""
+    sp = gpus // fsdp
+    lo, hi = 0, 1 << 24
+    while hi - lo > 1024:
+        mid = (lo + hi) // 2 // 1024 * 1024
+        if bytes_per_gpu(cfg, mid, sp, fsdp)["total"] <= hbm_bytes * (1 - reserve):
+            lo = mid
+        else:
+            hi = mid
+    return lo * sp
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    ap.add_argument("--model", default="llama-7b")
+    ap.add_argument("--gpus", type=int, nargs="+", default=[1, 2, 4, 8])
+    ap.add_argument("--fsdp", type=int, default=1)
+    args = ap.parse_args(argv)
+    cfg = LlamaConfig.named(args.model)
+    for g in args.gpus:
+        ctx = max_context(cfg, g, fsdp=args.fsdp)
+        b = bytes_per_gpu(cfg, ctx // max(1, g // args.fsdp), g // args.fsdp, args.fsdp)
+        print(json.dumps({"gpus": g, "fsdp": args.fsdp, "max_context_tokens": ctx,
+                          "gib_per_gpu": {k: round(v / GiB, 1) for k, v in b.items()}}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
