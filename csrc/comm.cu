@@ -16,9 +16,13 @@
 namespace ra {
 namespace comm {
 
+// `epoch_ptr` (optional, local device memory) replaces the host-supplied epoch: the kernel uses
+// *epoch_ptr + 1 and stores it back, so a launch recorded in a CUDA graph works on every replay.
 __global__ void barrier_kernel(uint32_t* const* __restrict__ peer_flags, int rank, int n, uint32_t epoch,
-                               unsigned long long timeout_ns, int* status) {
+                               unsigned long long timeout_ns, int* status, uint32_t* epoch_ptr) {
   const int t = threadIdx.x;
+  if (epoch_ptr) epoch = *epoch_ptr + 1;
+  __syncthreads();
   if (t < n) {
     __threadfence_system();
     uint32_t* remote = peer_flags[t] + rank;
@@ -38,6 +42,8 @@ __global__ void barrier_kernel(uint32_t* const* __restrict__ peer_flags, int ran
     }
     __threadfence_system();
   }
+  __syncthreads();
+  if (epoch_ptr && t == 0) *epoch_ptr = epoch;
 }
 
 __global__ void copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
@@ -106,13 +112,14 @@ extern "C" int ra_ipc_close(void* p) {
 
 // peer_flags: device array of n pointers (one per rank, in this process' address space).
 extern "C" int ra_symm_barrier(void* const* peer_flags, int rank, int n, unsigned int epoch,
-                               unsigned long long timeout_ns, int* status, void* stream) {
+                               unsigned long long timeout_ns, int* status, void* stream,
+                               unsigned int* epoch_ptr) {
   if (n < 1 || n > 32 || rank < 0 || rank >= n) {
     set_error("ra_symm_barrier: bad rank/size");
     return kHostBadArg;
   }
   comm::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<uint32_t* const*>(peer_flags), rank, n, epoch, timeout_ns, status);
+      reinterpret_cast<uint32_t* const*>(peer_flags), rank, n, epoch, timeout_ns, status, epoch_ptr);
   return check_launch("barrier_kernel");
 }
 

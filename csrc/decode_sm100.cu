@@ -38,6 +38,8 @@ struct SplitParams {
   float scale_log2;
   long long q_pos0;  // global position of query row 0, or < 0 for no causal rule
   long long k_pos0;  // global position of local cache row 0
+  const long long* pos_ptr;  // optional: the query position lives on the device (CUDA-graph decode);
+                             // then q_pos0 = *pos_ptr and the rows to visit are [0, min(S, *pos_ptr + 1 - k_pos0))
 };
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
@@ -78,8 +80,17 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
     for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
   }
 
-  const int r0 = split * p.rows_per_split;
-  const int r1 = min(p.S, r0 + p.rows_per_split);
+  long long q_pos0 = p.q_pos0;
+  int S = p.S, rows_per_split = p.rows_per_split;
+  if (p.pos_ptr) {
+    q_pos0 = *p.pos_ptr;
+    const long long n = q_pos0 + 1 - p.k_pos0;
+    S = static_cast<int>(n < 0 ? 0 : (n > p.S ? p.S : n));
+    rows_per_split = (S + p.splits - 1) / p.splits;
+    if (rows_per_split < 1) rows_per_split = 1;
+  }
+  const int r0 = split * rows_per_split;
+  const int r1 = min(S, r0 + rows_per_split);
   const __nv_bfloat16* kb = p.k + b * p.k_sb + h * p.k_sh + dl * 8;
   const __nv_bfloat16* vb = p.v + b * p.v_sb + h * p.v_sh + dl * 8;
   const int step = WARPS * RPW;
@@ -116,7 +127,7 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
         bool vis = ok[u];
-        if (p.q_pos0 >= 0) vis = vis && (p.k_pos0 + r <= p.q_pos0 + i);
+        if (q_pos0 >= 0) vis = vis && (p.k_pos0 + r <= q_pos0 + i);
         if (p.mask && vis)
           vis = p.mask[b * p.m_sb + h * p.m_sh + i * p.m_sq + r] != 0;
         s[u][i] = vis ? d : -INFINITY;
@@ -206,12 +217,21 @@ struct MergeParams {
   float* const* inbox_o;    // [n_ranks] pointers to (rows, n_ranks, D)
   float* const* inbox_lse;  // [n_ranks] pointers to (rows, n_ranks)
   int n_ranks, my_rank;
+  // optional double-buffer selection from a device-side step counter (CUDA-graph decode): slot =
+  // (*step_ptr * slot_mul + slot_add) & 1 is applied to the inbox stores (out_slot_*) and to the partials read
+  // (in_slot_*): slot_mul = exchanges per decode step, slot_add = index of this exchange within the step, so
+  // that consecutive exchanges always alternate slots
+  const long long* step_ptr;
+  long long slot_mul, slot_add;
+  long long out_slot_o, out_slot_l, in_slot_o, in_slot_l;  // strides in floats
 };
 
 // One CTA per row = (b, h, i); D threads.
 __global__ void decode_merge_kernel(const MergeParams p) {
   const int row = blockIdx.x, d = threadIdx.x;
-  const float* lp = p.lse_part + static_cast<long long>(row) * p.l_rs;
+  const long long slot = p.step_ptr ? ((*p.step_ptr * p.slot_mul + p.slot_add) & 1) : 0;
+  const float* o_in = p.o_part + slot * p.in_slot_o;
+  const float* lp = p.lse_part + slot * p.in_slot_l + static_cast<long long>(row) * p.l_rs;
   float mx = -INFINITY;
   for (int s = 0; s < p.nparts; ++s) mx = fmaxf(mx, lp[s * p.l_ps]);
   float wsum = 0.f, o = 0.f;
@@ -219,15 +239,15 @@ __global__ void decode_merge_kernel(const MergeParams p) {
     for (int s = 0; s < p.nparts; ++s) {
       const float w = __expf(lp[s * p.l_ps] - mx);
       wsum += w;
-      o += w * p.o_part[static_cast<long long>(row) * p.o_rs + s * p.o_ps + d];
+      o += w * o_in[static_cast<long long>(row) * p.o_rs + s * p.o_ps + d];
     }
     o /= wsum;
   }
   const float lse = mx == -INFINITY ? -INFINITY : mx + __logf(wsum);
   if (p.inbox_o) {
     for (int r = 0; r < p.n_ranks; ++r) {
-      p.inbox_o[r][(static_cast<long long>(row) * p.n_ranks + p.my_rank) * p.D + d] = o;
-      if (d == 0) p.inbox_lse[r][static_cast<long long>(row) * p.n_ranks + p.my_rank] = lse;
+      p.inbox_o[r][slot * p.out_slot_o + (static_cast<long long>(row) * p.n_ranks + p.my_rank) * p.D + d] = o;
+      if (d == 0) p.inbox_lse[r][slot * p.out_slot_l + static_cast<long long>(row) * p.n_ranks + p.my_rank] = lse;
     }
     __threadfence_system();
   }
@@ -244,6 +264,24 @@ __global__ void decode_merge_kernel(const MergeParams p) {
       reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16(o);
   }
   if (p.lse_out && d == 0) p.lse_out[row] = lse;
+}
+
+// Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to
+// cache row (*pos_ptr - k0) of this rank's (B, S_max, 2, H, D) shard if that position is local.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ cache,
+                                 const long long* __restrict__ pos_ptr, long long k0, int S_max, int HD) {
+  const long long r = *pos_ptr - k0;
+  if (r < 0 || r >= S_max) return;
+  const int b = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(b) * 3 + 1) * HD);
+  uint4* dst = reinterpret_cast<uint4*>(cache + ((static_cast<long long>(b) * S_max + r) * 2) * HD);
+  for (int i = threadIdx.x; i < 2 * HD / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// state = {position, step}: advanced once per decoded token.
+__global__ void decode_advance_kernel(long long* state) {
+  state[0] += 1;
+  state[1] += 1;
 }
 
 // y[M, N] = x[M, K] W[N, K]^T for a handful of rows (M <= 8): one warp per output column, the
@@ -297,6 +335,7 @@ struct RaDecodeArgs {
   int B, H, QL, S, D, splits;
   float softmax_scale;
   long long q_pos0, k_pos0;
+  const long long* pos_ptr;
   void* stream;
 };
 
@@ -324,6 +363,7 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.q_pos0 = a->q_pos0;
   p.k_pos0 = a->k_pos0;
+  p.pos_ptr = a->pos_ptr;
   dim3 grid(a->splits, a->H, a->B);
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);
 #define RA_LAUNCH_DEC(DD, QQ) decode_splitkv_kernel<DD, QQ><<<grid, THREADS, 0, s>>>(p)
@@ -347,7 +387,9 @@ extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long 
                                long long l_rs, long long l_ps, int rows, int nparts, int D, int H,
                                int QL, void* out, int out_fp32, float* lse_out,
                                void* const* inbox_o, void* const* inbox_lse, int n_ranks, int my_rank,
-                               void* stream) {
+                               const long long* step_ptr, long long slot_mul, long long slot_add,
+                               long long out_slot_o, long long out_slot_l,
+                               long long in_slot_o, long long in_slot_l, void* stream) {
   using namespace ra::decode;
   if (rows < 1 || nparts < 1 || (D != 64 && D != 128)) {
     set_error("ra_decode_merge: bad shape");
@@ -361,8 +403,25 @@ extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long 
   p.inbox_o = reinterpret_cast<float* const*>(inbox_o);
   p.inbox_lse = reinterpret_cast<float* const*>(inbox_lse);
   p.n_ranks = n_ranks; p.my_rank = my_rank;
+  p.step_ptr = step_ptr;
+  p.slot_mul = slot_mul; p.slot_add = slot_add;
+  p.out_slot_o = out_slot_o; p.out_slot_l = out_slot_l; p.in_slot_o = in_slot_o; p.in_slot_l = in_slot_l;
   decode_merge_kernel<<<rows, D, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_launch("decode_merge_kernel");
+}
+
+extern "C" int ra_kv_append(const void* qkv, void* cache, const long long* pos_ptr, long long k0, int S_max,
+                            int B, int HD, void* stream) {
+  using namespace ra::decode;
+  if (HD % 8 || B < 1 || !pos_ptr) { set_error("ra_kv_append: bad arguments"); return kHostBadArg; }
+  kv_append_kernel<<<B, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(cache), pos_ptr, k0, S_max, HD);
+  return check_launch("kv_append_kernel");
+}
+
+extern "C" int ra_decode_advance(long long* state, void* stream) {
+  ra::decode::decode_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(state);
+  return check_launch("decode_advance_kernel");
 }
 
 extern "C" int ra_small_m_linear(const void* x, const void* w, void* y, const void* res, int M, int N,

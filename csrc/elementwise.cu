@@ -161,7 +161,8 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
 // pos = two-run position map of the local token index (see attn PosMap). sign = +1 fwd, -1 bwd.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long sb, long long ss, long long sh,
                             int B, int S, int H, int D, int off0, int off1, int half, float log2_theta,
-                            float sign) {
+                            float sign, const long long* __restrict__ pos_ptr) {
+  if (pos_ptr) off0 += static_cast<int>(*pos_ptr);  // position kept on the device (decode under a CUDA graph)
   const int hd2 = D >> 1;
   const int vec_per_row = hd2 >> 3;  // 8-element vectors in the first half
   const long long total = static_cast<long long>(B) * S * H * vec_per_row;
@@ -469,8 +470,18 @@ extern "C" int ra_rope(void* x, long long sb, long long ss, long long sh, int B,
   if (D % 16 || B <= 0 || S <= 0) { set_error("rope: head_dim must be a multiple of 16"); return kHostBadArg; }
   const long long work = static_cast<long long>(B) * S * H * (D / 16);
   rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<bf16*>(x), sb, ss, sh, B, S, H, D, off0, off1, half, log2f(theta), inverse ? -1.f : 1.f);
+      static_cast<bf16*>(x), sb, ss, sh, B, S, H, D, off0, off1, half, log2f(theta), inverse ? -1.f : 1.f, nullptr);
   return check_launch("rope");
+}
+
+// Same rotation with the position of token 0 read from device memory (off0 is added to it).
+extern "C" int ra_rope_at(void* x, long long sb, long long ss, long long sh, int B, int S, int H, int D,
+                          int off0, const long long* pos_ptr, float theta, void* stream) {
+  if (D % 16 || B <= 0 || S <= 0 || !pos_ptr) { set_error("rope_at: bad arguments"); return kHostBadArg; }
+  const long long work = static_cast<long long>(B) * S * H * (D / 16);
+  rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<bf16*>(x), sb, ss, sh, B, S, H, D, off0, 0, 1 << 30, log2f(theta), 1.f, pos_ptr);
+  return check_launch("rope_at");
 }
 
 extern "C" int ra_swiglu_fwd(const void* gu, void* h, long long rows, int F, void* stream) {

@@ -54,6 +54,11 @@ class LlamaInference:
         self.cache = [torch.zeros(batch, self.S_max, 2, self.H, self.D, device=self.device, dtype=torch.bfloat16)
                       for _ in range(cfg.n_layers)]
         self.length = 0                             # tokens in the cache (global)
+        # [position, step] on the device: lets one recorded CUDA graph serve every decode step
+        self.state = torch.zeros(2, dtype=torch.int64, device=self.device)
+        self._graph = None
+        self._tok_buf = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._logits_buf = None
 
     # ------------------------------------------------------------------ helpers
     def _n_local(self, total: int) -> int:
@@ -147,33 +152,58 @@ class LlamaInference:
         return out
 
     # ------------------------------------------------------------------ decode
-    @torch.no_grad()
-    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """One token per sequence: ``tokens (B,)`` -> logits ``(B, vocab)`` fp32 (same on all ranks)."""
+    def _decode_body(self, tokens: torch.Tensor) -> torch.Tensor:
+        """All launches of one decode step. Every per-token scalar (position, valid cache rows, inbox
+        slot, barrier count) is read from device memory, so the sequence can be graph-captured."""
         cfg, P = self.cfg, self.params
         B, H, D, d = self.B, self.H, self.D, self.d
-        pos = self.length
-        x = K.embedding_fwd(tokens.to(self.device, torch.int32).reshape(-1).contiguous(), P.w("embed"))
-        n_local = self._n_local(pos + 1)
+        x = K.embedding_fwd(tokens, P.w("embed"))
         for l in range(cfg.n_layers):
             h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
             qkv = K.linear_auto(h1, P.w(f"l{l}.wqkv"))
-            K.rope_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], Positions(pos), cfg.rope_theta)
-            qkv5 = qkv.view(B, 1, 3, H, D)
-            self._store_kv(l, qkv5[:, :, 1], qkv5[:, :, 2], pos)
+            K.rope_at_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], self.state, cfg.rope_theta)
+            K.kv_append(qkv, self.cache[l], self.state, self.k0)
             c = self.cache[l]
-            attn = Dk.ring_decode_attention(qkv5[:, :, 0].contiguous(), c[:, :, 0], c[:, :, 1], None, self.axis,
-                                            self.symm_ring, n_valid=n_local, q_pos0=pos, k_pos0=self.k0)
+            attn = Dk.ring_decode_attention(qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous(), c[:, :, 0], c[:, :, 1],
+                                            None, self.axis, self.symm_ring, k_pos0=self.k0, state=self.state,
+                                            exchange=l, exchanges_per_step=cfg.n_layers)
             x = K.linear_auto(attn.reshape(B, d), P.w(f"l{l}.wo"), residual=x)
             h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
             gu = K.linear_auto(h2, P.w(f"l{l}.wgu"))
             x = K.linear_auto(K.swiglu_fwd(gu), P.w(f"l{l}.wd"), residual=x)
-        self.length = pos + 1
         hf, _ = K.rmsnorm_fwd(x, P.w("nf"), cfg.rms_eps)
-        return K.linear_auto(hf, P.w("lm_head")).float()
+        logits = K.linear_auto(hf, P.w("lm_head")).float()
+        K.decode_advance(self.state)
+        return logits
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, new_tokens: int, chunk: int = 32768):
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One token per sequence: ``tokens (B,)`` -> logits ``(B, vocab)`` fp32 (same on all ranks)."""
+        self.state[0] = self.length
+        logits = self._decode_body(tokens.to(self.device, torch.int32).reshape(-1).contiguous())
+        self.length += 1
+        return logits
+
+    @torch.no_grad()
+    def decode_step_graph(self) -> torch.Tensor:
+        """Greedy step on the token in ``self._tok_buf`` through a CUDA graph recorded on first use:
+        one replay per token instead of ~15 launches per layer. Writes the next token back into
+        ``self._tok_buf`` and returns it. Call :meth:`decode_step` at least once before (buffers and
+        kernels must exist before capture)."""
+        if self._graph is None:
+            self.state[0] = self.length
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                logits = self._decode_body(self._tok_buf)
+                self._tok_buf.copy_(logits.argmax(dim=-1).to(torch.int32))
+            self._graph = g
+        self._graph.replay()
+        self.length += 1
+        return self._tok_buf
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, new_tokens: int, chunk: int = 32768, use_graph: bool = True):
         """Chunked prefill of ``prompt (B, T)`` followed by greedy decoding. Returns the generated
         tokens ``(B, new_tokens)`` and timing: prefill seconds, per-token decode latencies."""
         B, T = prompt.shape
@@ -187,13 +217,17 @@ class LlamaInference:
         out: List[torch.Tensor] = []
         lat: List[float] = []
         nxt = logits.argmax(dim=-1)
-        for _ in range(new_tokens):
-            out.append(nxt)
+        for i in range(new_tokens):
+            out.append(nxt.clone())
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            logits = self.decode_step(nxt)
-            nxt = logits.argmax(dim=-1)
+            if use_graph and i >= 2:
+                if i == 2:
+                    self._tok_buf.copy_(nxt.to(torch.int32))
+                nxt = self.decode_step_graph()
+            else:
+                nxt = self.decode_step(nxt).argmax(dim=-1)
             e1.record()
             torch.cuda.synchronize()
             lat.append(e0.elapsed_time(e1))
-        return torch.stack(out, dim=1), {"prefill_s": t_prefill, "decode_ms": lat}
+        return torch.stack([t.to(torch.int64) for t in out], dim=1), {"prefill_s": t_prefill, "decode_ms": lat}

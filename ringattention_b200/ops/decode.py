@@ -28,6 +28,7 @@ class _DecodeArgs(ctypes.Structure):
         ("D", ctypes.c_int), ("splits", ctypes.c_int),
         ("softmax_scale", ctypes.c_float),
         ("q_pos0", c_ll), ("k_pos0", c_ll),
+        ("pos_ptr", c_vp),
         ("stream", c_vp),
     ]
 
@@ -52,7 +53,7 @@ def default_splits(S: int, B: int, H: int) -> int:
 
 
 def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, k_pos0: int = 0,
-                   mask: Optional[torch.Tensor] = None, splits: Optional[int] = None):
+                   mask: Optional[torch.Tensor] = None, splits: Optional[int] = None, pos_ptr: int = 0):
     """Split-KV pass over this rank's cache rows ``[0, n_valid)``. Returns fp32 partials
     ``(o_part (B*H*QL, splits, D), lse_part (B*H*QL, splits), QL_padded)``."""
     B, QL, H, D = q.shape
@@ -75,12 +76,14 @@ def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, 
     a.B, a.H, a.QL, a.S, a.D, a.splits = B, H, QL, S, D, splits
     a.softmax_scale = 1.0 / math.sqrt(D)
     a.q_pos0, a.k_pos0 = int(q_pos0), int(k_pos0)
+    a.pos_ptr = pos_ptr
     a.stream = torch.cuda.current_stream().cuda_stream
     _lib.call("ra_decode_splitkv", ctypes.byref(a))
     return o_part, lse_part
 
 
-def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None, inbox=None):
+def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None, inbox=None,
+                   step_ptr: int = 0, slot_mul: int = 1, slot_add: int = 0, out_slot=(0, 0), in_slot=(0, 0)):
     """Merge ``nparts`` partials per row; ``o_part (rows, nparts, D)`` and ``lse_part (rows, nparts)``
     may be strided views. ``QL = 0`` writes rows in their own order (prefill); ``QL > 0`` maps row
     ``(b, h, i)`` to ``out[b, i, h]`` (decode). ``inbox = (o_ptrs, lse_ptrs, n_ranks, my_rank)`` makes the
@@ -97,12 +100,14 @@ def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None,
               c_vp(0 if out is None else out.data_ptr()),
               0 if out is None else int(out.dtype == torch.float32),
               c_vp(0 if lse_out is None else lse_out.data_ptr()), c_vp(o_ptrs), c_vp(lse_ptrs),
-              n_ranks, my_rank, _lib.stream_ptr())
+              n_ranks, my_rank, c_vp(step_ptr), c_ll(slot_mul), c_ll(slot_add), c_ll(out_slot[0]), c_ll(out_slot[1]), c_ll(in_slot[0]),
+              c_ll(in_slot[1]), _lib.stream_ptr())
     return out
 
 
 def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: Optional[int] = None,
-                          q_pos0: int = -1, k_pos0: Optional[int] = None):
+                          q_pos0: int = -1, k_pos0: Optional[int] = None, state: Optional[torch.Tensor] = None,
+                          exchange: int = 0, exchanges_per_step: int = 1):
     """``q (B, q_len<=8, H, D)`` replicated; ``k, v (B, kv_len, H, D)`` local cache shard; boolean
     ``attn_mask`` broadcastable to ``(B, H, q_len, S_total)``, global on the last axis (True =
     attend). Returns ``(B, q_len, H, D)`` in ``v.dtype``, identical on every rank."""
@@ -122,7 +127,10 @@ def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: 
         mask_u8 = m.to(torch.uint8).contiguous()
     if k_pos0 is None:
         k_pos0 = rank * S_loc
-    o_part, lse_part = decode_partial(qp, k, v, n_valid=n_valid, q_pos0=q_pos0, k_pos0=k_pos0, mask=mask_u8)
+    pos_ptr = 0 if state is None else state.data_ptr()
+    step_ptr = 0 if state is None else state.data_ptr() + 8
+    o_part, lse_part = decode_partial(qp, k, v, n_valid=n_valid, q_pos0=q_pos0, k_pos0=k_pos0, mask=mask_u8,
+                                      pos_ptr=pos_ptr)
     out = torch.empty(B, QL, H, D, device=q.device, dtype=v.dtype)
     if world == 1:
         merge_partials(o_part, lse_part, H, QL, out=out)
@@ -132,14 +140,26 @@ def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: 
     rows = B * H * QL
     inbox_o = symm_ring.buffer("decode_inbox_o", 2 * rows * world * D * 4)
     inbox_l = symm_ring.buffer("decode_inbox_lse", 2 * rows * world * 4)
-    slot = symm_ring.calls & 1  # double-buffered across calls: one barrier per call is enough
-    symm_ring.calls += 1
-    off_o, off_l = slot * rows * world * D * 4, slot * rows * world * 4
-    o_ptrs = torch.tensor([p + off_o for p in inbox_o.peer_ptrs], dtype=torch.int64, device=q.device)
-    l_ptrs = torch.tensor([p + off_l for p in inbox_l.peer_ptrs], dtype=torch.int64, device=q.device)
-    merge_partials(o_part, lse_part, H, QL, inbox=(o_ptrs.data_ptr(), l_ptrs.data_ptr(), world, rank))
-    symm_ring.barrier()
-    io = inbox_o.local[off_o:off_o + rows * world * D * 4].view(torch.float32).view(rows, world, D)
-    il = inbox_l.local[off_l:off_l + rows * world * 4].view(torch.float32).view(rows, world)
-    merge_partials(io, il, H, QL, out=out)
+    o_tab, l_tab = symm_ring.peer_ptr_table("decode_inbox_o"), symm_ring.peer_ptr_table("decode_inbox_lse")
+    n_o, n_l = rows * world * D, rows * world  # floats per inbox slot
+    io = inbox_o.local.view(torch.float32)
+    il = inbox_l.local.view(torch.float32)
+    if state is None:
+        # double-buffered across calls (one barrier per call is enough); slot chosen on the host
+        slot = symm_ring.calls & 1
+        symm_ring.calls += 1
+        o_ptrs = o_tab + slot * n_o * 4
+        l_ptrs = l_tab + slot * n_l * 4
+        merge_partials(o_part, lse_part, H, QL, inbox=(o_ptrs.data_ptr(), l_ptrs.data_ptr(), world, rank))
+        symm_ring.barrier()
+        merge_partials(io[slot * n_o:(slot + 1) * n_o].view(rows, world, D),
+                       il[slot * n_l:(slot + 1) * n_l].view(rows, world), H, QL, out=out)
+    else:
+        # slot = (step * exchanges_per_step + exchange) & 1, from the device-side step counter
+        sk = dict(step_ptr=step_ptr, slot_mul=exchanges_per_step, slot_add=exchange)
+        merge_partials(o_part, lse_part, H, QL, inbox=(o_tab.data_ptr(), l_tab.data_ptr(), world, rank),
+                       out_slot=(n_o, n_l), **sk)
+        symm_ring.barrier()
+        merge_partials(io[:n_o].view(rows, world, D), il[:n_l].view(rows, world), H, QL, out=out,
+                       in_slot=(n_o, n_l), **sk)
     return out[:, :ql]

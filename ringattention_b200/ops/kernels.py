@@ -213,3 +213,25 @@ def linear_auto(x, w, out=None, residual=None):
             (residual is None or residual.is_contiguous()):
         return small_m_linear(x, w, out=out, residual=residual)
     return linear_fwd(x, w, out=out, residual=residual)
+
+
+def rope_at_(x, pos_state, theta: float, offset: int = 0):
+    """In-place RoPE of a ``(B, S, H, D)`` view whose first token sits at ``pos_state[0] + offset``,
+    with the position read from device memory (decode under a CUDA graph)."""
+    B, S, H, D = x.shape
+    _lib.call("ra_rope_at", ptr(x), c_ll(x.stride(0)), c_ll(x.stride(1)), c_ll(x.stride(2)), B, S, H, D,
+              int(offset), ptr(pos_state), c_f(theta), stream_ptr())
+    return x
+
+
+def kv_append(qkv, cache, pos_state, k0: int):
+    """Write the K/V rows of a one-token ``(B, 1, 3, H, D)`` qkv buffer into row ``pos - k0`` of the
+    contiguous ``(B, S_max, 2, H, D)`` cache shard when that position belongs to this rank."""
+    B, S_max, two, H, D = cache.shape
+    assert cache.is_contiguous() and qkv.is_contiguous() and two == 2
+    _lib.call("ra_kv_append", ptr(qkv), ptr(cache), ptr(pos_state), c_ll(k0), S_max, B, H * D, stream_ptr())
+
+
+def decode_advance(state):
+    """``state[0] += 1`` (position) and ``state[1] += 1`` (step) on the device."""
+    _lib.call("ra_decode_advance", ptr(state), stream_ptr())

@@ -100,12 +100,14 @@ class SymmRing:
                                                    timeout_s if timeout_s is not None else 120.0)) * 1e9)
         self.copy_ctas = copy_ctas
         self.overlap = True  # False: pull each block with a separate copy kernel before its step (for measurements)
-        self.epoch = 0
         self.calls = 0
         self._bufs: Dict[str, SymmBuffer] = {}
         self._local: Dict[str, torch.Tensor] = {}
         self.flags = SymmBuffer(256, group, self.device)
         self._flag_ptrs = torch.tensor(self.flags.peer_ptrs, dtype=torch.int64, device=self.device)
+        # barrier count kept on the device, so that a barrier recorded in a CUDA graph stays valid on replay
+        self._epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ptr_cache: Dict[str, tuple] = {}
         dist.barrier(group=group)
 
     # ------------------------------------------------------------------ plumbing
@@ -131,10 +133,19 @@ class SymmRing:
 
     def barrier(self) -> None:
         """Stream-ordered flag barrier across the ring; a missing peer ends in a status code."""
-        self.epoch += 1
         _lib.call("ra_symm_barrier", c_vp(self._flag_ptrs.data_ptr()), self.rank, self.size,
-                  ctypes.c_uint(self.epoch & 0xFFFFFFFF), ctypes.c_ulonglong(self.timeout_ns),
-                  c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr())
+                  ctypes.c_uint(0), ctypes.c_ulonglong(self.timeout_ns),
+                  c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr(),
+                  c_vp(self._epoch_dev.data_ptr()))
+
+    def peer_ptr_table(self, name: str) -> torch.Tensor:
+        """Device array with every rank's address of symmetric buffer ``name`` (cached)."""
+        b = self._bufs[name]
+        hit = self._ptr_cache.get(name)
+        if hit is None or hit[0] != b.ptr:  # (re)allocated since the table was built
+            hit = (b.ptr, torch.tensor(b.peer_ptrs, dtype=torch.int64, device=self.device))
+            self._ptr_cache[name] = hit
+        return hit[1]
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)

@@ -72,3 +72,22 @@ def test_prefill_and_greedy_decode_match_full_forward():
     ref_next = logits[:, T - 1:-1].argmax(-1)
     assert (ref_next == gen).float().mean() >= 0.9
     assert len(timing["decode_ms"]) == 8 and inf.length == T + 8
+
+
+def test_graph_replayed_decode_equals_eager_decode():
+    """The CUDA-graph decode path (device-side position/step) must emit the same tokens as the eager path."""
+    from ringattention_b200.config import LlamaConfig
+    from ringattention_b200.models.llama_infer import LlamaInference
+    from ringattention_b200.ops import _lib
+
+    cfg = LlamaConfig.named("llama-tiny")
+    torch.manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab_size, (2, 256), device="cuda")
+    a = LlamaInference(cfg, max_context=512, batch=2, seed=7)
+    b = LlamaInference(cfg, max_context=512, batch=2, seed=7)
+    ga, _ = a.generate(prompt, 12, chunk=128, use_graph=True)
+    gb, _ = b.generate(prompt, 12, chunk=128, use_graph=False)
+    _lib.check_status()
+    assert a._graph is not None and b._graph is None
+    assert torch.equal(ga, gb)
+    assert int(a.state[0].item()) == a.length == 256 + 12

@@ -106,7 +106,8 @@ def test_bounded_wait_reports_status_and_context_survives():
     flags = torch.zeros(2, 64, dtype=torch.int32, device="cuda")  # two "ranks", both local
     ptrs = torch.tensor([flags[0].data_ptr(), flags[1].data_ptr()], dtype=torch.int64, device="cuda")
     _lib.call("ra_symm_barrier", ctypes.c_void_p(ptrs.data_ptr()), 0, 2, ctypes.c_uint(1),
-              ctypes.c_ulonglong(50_000_000), ctypes.c_void_p(st.data_ptr()), _lib.stream_ptr())
+              ctypes.c_ulonglong(50_000_000), ctypes.c_void_p(st.data_ptr()), _lib.stream_ptr(),
+              ctypes.c_void_p(0))
     torch.cuda.synchronize()
     with pytest.raises(_lib.KernelError, match="peer flag"):
         _lib.check_status()
