@@ -366,7 +366,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (!tile_visible(mk, b, qi0, k0)) continue;
       const int st = it & 1;
       const uint32_t par = it & 1;
-      const bool plain = tile_plain(mk, qi0, k0);
+      const bool plain = tile_plain(mk, b, qi0, k0);
       if (mk.seg_q) {
         if (sm_tid < 128)
           sSegQ[st * 128 + sm_tid] =
@@ -407,24 +407,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           x[2 * g + 1] = f2_fma(f2_pack_u(s[4 * g + 2], s[4 * g + 3]), scale2, f2_pack(n.z, n.w));
         }
         if (!plain) {
+          // keepw bit e: column (q index) base+e survives the causal rule, padding and dropout; the hash is a
+          // small rolled loop that only runs when dropout is on
+          const int base = half * 64 + c * 32;
+          const int n = lo - base;
+          uint32_t keepw = n <= 0 ? 0xffffffffu : (n >= 32 ? 0u : ~((1u << n) - 1u));
+          if (mk.drop_threshold) {
+            uint32_t drop = 0;
+#pragma unroll 1
+            for (int e = 0; e < 32; ++e)
+              drop |= static_cast<uint32_t>(dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + base + e,
+                                                         static_cast<unsigned int>(kpos)) < mk.drop_threshold)
+                      << e;
+            keepw &= ~drop;
+          }
+          const bool has_seg = mk.seg_q != nullptr;
+          const int4* seg4 = reinterpret_cast<const int4*>(sSegQ + st * 128 + base);
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            x[e] = f2_add(x[e], bias2);
-            float x0, x1;
-            f2_unpack(x[e], x0, x1);
-            const int col = half * 64 + c * 32 + 2 * e;
-            bool m0 = col < lo, m1 = (col + 1) < lo;
-            if (mk.seg_q) {
-              m0 |= (sSegQ[st * 128 + col] != my_seg);
-              m1 |= (sSegQ[st * 128 + col + 1] != my_seg);
+          for (int g = 0; g < 8; ++g) {
+            const int4 sg = has_seg ? seg4[g] : make_int4(my_seg, my_seg, my_seg, my_seg);
+            const int se[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int e = 2 * g + h2;
+              x[e] = f2_add(x[e], bias2);
+              float x0, x1;
+              f2_unpack(x[e], x0, x1);
+              const bool m0 = (((keepw >> (2 * e)) & 1u) == 0u) || (se[2 * h2] != my_seg);
+              const bool m1 = (((keepw >> (2 * e + 1)) & 1u) == 0u) || (se[2 * h2 + 1] != my_seg);
+              x[e] = f2_pack(m0 ? -INFINITY : x0, m1 ? -INFINITY : x1);
             }
-            if (mk.drop_threshold) {
-              m0 |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + col,
-                                 static_cast<unsigned int>(kpos)) < mk.drop_threshold;
-              m1 |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, qpos0 + col + 1,
-                                 static_cast<unsigned int>(kpos)) < mk.drop_threshold;
-            }
-            x[e] = f2_pack(m0 ? -INFINITY : x0, m1 ? -INFINITY : x1);
           }
         }
         uint32_t pk[16];

@@ -50,10 +50,20 @@ __device__ __forceinline__ bool tile_visible(const MaskParams& m, int b, int qi0
   return true;
 }
 
-// True when no entry of the tile needs element-wise masking or bias.
-__device__ __forceinline__ bool tile_plain(const MaskParams& m, int qi0, int k0) {
-  if (m.seg_q || m.bias || m.drop_threshold) return false;
-  if (k0 + 128 > m.Sk) return false;
+// True when no entry of the tile needs element-wise masking or bias. With segment ids that is the case
+// when both tiles lie inside one and the same segment (per-tile min == max, equal on both sides), which
+// holds for most tiles of packed documents much longer than a tile.
+__device__ __forceinline__ bool tile_plain(const MaskParams& m, int b, int qi0, int k0) {
+  if (m.bias || m.drop_threshold) return false;
+  if (k0 + 128 > m.Sk || qi0 + 128 > m.Sq) return false;
+  if (m.seg_q) {
+    if (!m.seg_q_mm) return false;
+    const int nqt = (m.Sq + 127) >> 7, nkt = (m.Sk + 127) >> 7;
+    const int* qm = m.seg_q_mm + (static_cast<long long>(b) * nqt + (qi0 >> 7)) * 2;
+    const int* km = m.seg_k_mm + (static_cast<long long>(b) * nkt + (k0 >> 7)) * 2;
+    const int q_lo = qm[0], k_lo = km[0];
+    if (q_lo != qm[1] || k_lo != km[1] || q_lo != k_lo) return false;
+  }
   if (m.cbs == 1) {
     if (m.qmap(qi0) < m.kmap(min(k0 + 127, m.Sk - 1))) return false;
   } else if (m.cbs) {

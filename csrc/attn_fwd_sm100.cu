@@ -309,7 +309,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const int k0 = j * 128;
       // the predicate is evaluated for both tiles by every role so that skips stay consistent
       if (!tile_visible(mk, b, qi0, k0)) continue;
-      const bool plain = tile_plain(mk, qi0, k0);
+      const bool plain = tile_plain(mk, b, qi0, k0);
       if (!plain && (mk.seg_k || mk.bias)) {
         const int buf = cnt & 1;
         const int kc = k0 + wg_tid;
@@ -345,23 +345,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
         mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3])) * sc;
       } else {
+        // keep[c] bit i: column 32c+i survives the causal rule, the sequence end and dropout. Built apart
+        // from the element loop so that the (large) hash code is a small rolled loop that only runs when
+        // dropout is on; the element loop itself stays a handful of instructions per column.
         const int limit = causal_col_limit(mk, qpos, k0);
-        const int* segb = sSeg + (w * 2 + (cnt & 1)) * 128;
-        const float* biasb = sBias + (w * 2 + (cnt & 1)) * 128;
-        const unsigned int kpos0 = static_cast<unsigned int>(mk.kmap(k0));
+        uint32_t keep[4];
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          float x = __uint_as_float(sr[i]) * sc;
-          if (mk.bias) x += biasb[i];
-          bool masked = i >= limit;
-          if (mk.seg_k) masked |= (segb[i] != my_seg);
-          if (mk.drop_threshold)
-            masked |= dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, static_cast<unsigned int>(qpos),
-                                   kpos0 + i) < mk.drop_threshold;
-          x = masked ? -INFINITY : x;
-          sr[i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+        for (int c = 0; c < 4; ++c) {
+          const int n = limit - 32 * c;
+          keep[c] = n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
         }
+        if (mk.drop_threshold) {
+          const unsigned int kpos0 = static_cast<unsigned int>(mk.kmap(k0));
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t drop = 0;
+#pragma unroll 1
+            for (int i = 0; i < 32; ++i)
+              drop |= static_cast<uint32_t>(dropout_hash(mk.seed_lo, mk.seed_hi, bh_u, static_cast<unsigned int>(qpos),
+                                                         kpos0 + c * 32 + i) < mk.drop_threshold)
+                      << i;
+            keep[c] &= ~drop;
+          }
+        }
+        const bool has_seg = mk.seg_k != nullptr, has_bias = mk.bias != nullptr;
+        const int4* seg4 = reinterpret_cast<const int4*>(sSeg + (w * 2 + (cnt & 1)) * 128);
+        const float4* bias4 = reinterpret_cast<const float4*>(sBias + (w * 2 + (cnt & 1)) * 128);
+        float mc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int g = 0; g < 32; ++g) {
+          const int4 sg = has_seg ? seg4[g] : make_int4(my_seg, my_seg, my_seg, my_seg);
+          const float4 bs = has_bias ? bias4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+          const int se[4] = {sg.x, sg.y, sg.z, sg.w};
+          const float be[4] = {bs.x, bs.y, bs.z, bs.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = 4 * g + e;
+            float x = fmaf(__uint_as_float(sr[i]), sc, be[e]);
+            const bool masked = (((keep[i >> 5] >> (i & 31)) & 1u) == 0u) || (se[e] != my_seg);
+            x = masked ? -INFINITY : x;
+            sr[i] = __float_as_uint(x);
+            mc[e] = fmaxf(mc[e], x);
+          }
+        }
+        mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
         sc = 1.0f;
       }
 

@@ -23,6 +23,7 @@ from ..ops import attention as A
 from ..ops import kernels as K
 from ..ops.flash import Positions
 from ..ops.reference import shard_segments
+from ..utils.tracing import phase
 from .params import FlatParams
 
 
@@ -73,7 +74,8 @@ class LlamaModel:
         qk = qkv.view(B, S, 3 * H, D)[:, :, :2 * H]  # q heads then k heads
         K.rope_(qk, ctx.positions, cfg.rope_theta)
         q, k, v = qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]
-        attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
+        with phase("attn_fwd"):
+            attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
         x2 = P.lin_fwd(attn.view(B * S, d), f"l{l}.wo", residual=x)
         return x2, (h1, rstd1, qkv, attn, lse)
 
@@ -128,8 +130,9 @@ class LlamaModel:
         qkv5 = qkv.view(B, S, 3, H, D)
         dqkv = torch.empty_like(qkv)
         dqkv5 = dqkv.view(B, S, 3, H, D)
-        A.ring_backward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], attn, lse, dattn.view(B, S, H, D),
-                        ctx.plan, ctx.symm_ring, dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
+        with phase("attn_bwd"):
+            A.ring_backward(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], attn, lse, dattn.view(B, S, H, D),
+                            ctx.plan, ctx.symm_ring, dq=dqkv5[:, :, 0], dk=dqkv5[:, :, 1], dv=dqkv5[:, :, 2])
         K.rope_(dqkv.view(B, S, 3 * H, D)[:, :, :2 * H], ctx.positions, cfg.rope_theta, inverse=True)
         P.lin_wgrad(dqkv, h1, f"l{l}.wqkv")
         dh1 = P.lin_dgrad(dqkv, f"l{l}.wqkv")
@@ -178,7 +181,8 @@ class LlamaModel:
             layer_inputs.append(x)
             x, saved = self.layer_forward(l, x, ctx, keep=keep)
             saved_all.append(saved)
-        loss_sum, dx = self.head_forward_backward(x, targets, ctx)
+        with phase("head"):
+            loss_sum, dx = self.head_forward_backward(x, targets, ctx)
         del x
         for l in reversed(range(cfg.n_layers)):
             dx = self.layer_backward(l, layer_inputs[l], dx, ctx, saved_all[l])

@@ -24,6 +24,7 @@ import torch.distributed as dist
 from ..config import LlamaConfig
 from ..ops import _lib
 from ..ops import kernels as K
+from ..utils.tracing import phase
 
 c_ll = ctypes.c_longlong
 c_vp = ctypes.c_void_p
@@ -207,37 +208,40 @@ class FlatParams:
     def lin_fwd(self, x, name: str, out=None, residual=None):
         """``y = x W^T (+ residual)``."""
         off, N, Kd, sr = self.mat[name]
-        if self.shard_count == 1:
-            return K.linear_fwd(x, self.w(name), out=out, residual=residual)
-        M = x.shape[0]
-        if out is None:
-            out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
-        return self._gather_call(x, name, 0, out, residual, M, N, Kd)
+        with phase("linear"):
+            if self.shard_count == 1:
+                return K.linear_fwd(x, self.w(name), out=out, residual=residual)
+            M = x.shape[0]
+            if out is None:
+                out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+            return self._gather_call(x, name, 0, out, residual, M, N, Kd)
 
     def lin_dgrad(self, dy, name: str, out=None, residual=None):
         """``dx = dy W (+ residual)``."""
         off, N, Kd, sr = self.mat[name]
-        if self.shard_count == 1:
-            return K.linear_dgrad(dy, self.w(name), out=out, residual=residual)
-        M = dy.shape[0]
-        if out is None:
-            out = torch.empty(M, Kd, device=dy.device, dtype=torch.bfloat16)
-        return self._gather_call(dy, name, 1, out, residual, M, Kd, N)
+        with phase("linear"):
+            if self.shard_count == 1:
+                return K.linear_dgrad(dy, self.w(name), out=out, residual=residual)
+            M = dy.shape[0]
+            if out is None:
+                out = torch.empty(M, Kd, device=dy.device, dtype=torch.bfloat16)
+            return self._gather_call(dy, name, 1, out, residual, M, Kd, N)
 
     def lin_wgrad(self, dy, x, name: str) -> None:
         """``dW += dy^T x`` (fp32). With sharding, each shard's rows are a GEMM of their own, written
         into that shard's segment of the gradient buffer."""
         off, N, Kd, sr = self.mat[name]
-        if self.shard_count == 1:
-            K.linear_wgrad(dy, x, self.g(name))
-            return
-        for s in range(self.shard_count):
-            r0 = s * sr
-            rows = max(0, min(sr, N - r0))
-            if rows == 0:
-                continue
-            acc = self.grad_shard(s)[off:off + rows * Kd].view(rows, Kd)
-            K.gemm(dy[:, r0:r0 + rows], x, a_mn=True, b_mn=True, out=acc, residual=acc)
+        with phase("wgrad"):
+            if self.shard_count == 1:
+                K.linear_wgrad(dy, x, self.g(name))
+                return
+            for s in range(self.shard_count):
+                r0 = s * sr
+                rows = max(0, min(sr, N - r0))
+                if rows == 0:
+                    continue
+                acc = self.grad_shard(s)[off:off + rows * Kd].view(rows, Kd)
+                K.gemm(dy[:, r0:r0 + rows], x, a_mn=True, b_mn=True, out=acc, residual=acc)
 
     # ------------------------------------------------------------------ optimizer
     def adamw_step(self, step: int, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,

@@ -20,6 +20,7 @@ from .ops import _lib
 from .ops import kernels as K
 from .ops.reference import shard_positions
 from .parallel.mesh import DeviceMesh
+from .utils.tracing import phase
 
 
 def init_distributed(backend: Optional[str] = None) -> Tuple[int, int, int]:
@@ -159,12 +160,15 @@ class Trainer:
         """Forward/backward, gradient reduction and optimizer update on device-resident inputs.
         Returns the global mean loss as a 0-d device tensor."""
         P = self.model.params
-        P.ensure_grads().zero_()
-        loss_sum = self.model.forward_backward(tok_dev, tgt_dev, ctx)
-        if self.world > 1:
-            dist.all_reduce(loss_sum)
-            self._all_reduce_grads()
-        self.optimizer_step()
+        with phase("step_total"):
+            P.ensure_grads().zero_()
+            loss_sum = self.model.forward_backward(tok_dev, tgt_dev, ctx)
+            if self.world > 1:
+                with phase("grad_allreduce"):
+                    dist.all_reduce(loss_sum)
+                    self._all_reduce_grads()
+            with phase("optimizer"):
+                self.optimizer_step()
         return loss_sum / max(1, ctx.total_tokens)
 
     def _all_reduce_grads(self, bucket: int = 1 << 28) -> None:

@@ -73,6 +73,9 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--mean-doc-len", type=int, default=0,
+                    help="attention kernels: packed documents with geometric lengths of this mean (segment ids); "
+                         "-1 = segment ids present but all equal")
     args = ap.parse_args(argv)
     peak_tf, peak_gbs, how = peaks()
     torch.manual_seed(0)
@@ -86,6 +89,20 @@ def main(argv=None) -> int:
         out = torch.empty_like(q)
         lse = torch.empty(B, H, S, device=dev)
         frac = 0.5 if args.causal else 1.0
+        if args.mean_doc_len:
+            from ..trainer import geometric_segment_ids
+
+            if args.mean_doc_len > 0:
+                seg = geometric_segment_ids(B, S, args.mean_doc_len, torch.Generator().manual_seed(0)).to(dev)
+            else:
+                seg = torch.zeros(B, S, dtype=torch.int32, device=dev)
+            ms.seg_q = ms.seg_k = seg
+            ms.seg_q_mm = ms.seg_k_mm = flash.seg_tile_minmax(seg)
+            # visible (q, k) pairs: same document and (if causal) k <= q
+            ln = torch.bincount(seg.flatten().long() + (torch.arange(B, device=dev)[:, None] * (int(seg.max()) + 1)).expand(B, S).flatten()).double()
+            pairs = float(((ln * (ln + 1) / 2) if args.causal else ln * ln).sum())
+            frac = pairs / (float(B) * S * S)
+            res["visible_fraction"] = round(frac, 5)
         if args.kernel == "attn_fwd":
             fn = lambda: flash.flash_fwd(q, k, v, ms, out=out, lse_out=lse)
             flops = 4.0 * B * S * S * H * D * frac

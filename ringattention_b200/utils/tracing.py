@@ -36,6 +36,54 @@ def nvtx_range(name: str):
         yield
 
 
+class PhaseTimer:
+    """Device time per named phase of a step: a CUDA-event pair on the current stream around every
+    ``phase(name)`` region while the timer is installed. ``summary()`` synchronizes and returns the
+    milliseconds per phase (summed over the regions) and the number of regions."""
+
+    def __init__(self):
+        self._pairs = {}
+
+    def _add(self, name, e0, e1):
+        self._pairs.setdefault(name, []).append((e0, e1))
+
+    def summary(self, reset: bool = True) -> dict:
+        torch.cuda.synchronize()
+        out = {name: {"ms": round(sum(a.elapsed_time(b) for a, b in pairs), 3), "regions": len(pairs)}
+               for name, pairs in self._pairs.items()}
+        if reset:
+            self._pairs = {}
+        return out
+
+
+_TIMER = None
+
+
+def set_phase_timer(timer: "PhaseTimer | None") -> None:
+    """Install (or remove, with ``None``) the timer that :func:`phase` regions report to."""
+    global _TIMER
+    _TIMER = timer
+
+
+@contextlib.contextmanager
+def phase(name: str):
+    """Marks a host-side phase of a step (attention forward, linear layers, gradient reduction, ...):
+    an NVTX range when NVTX tracing is on, a CUDA-event pair when a :class:`PhaseTimer` is installed,
+    otherwise nothing."""
+    t = _TIMER
+    if t is None and not _ENABLED:
+        yield
+        return
+    if t is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    with nvtx_range(name):
+        yield
+    if t is not None:
+        e1.record()
+        t._add(name, e0, e1)
+
+
 ROLES = ("mma", "softmax", "drain")
 SLOTS = {
     "mma": ("dP issued", "p_ready seen", "ds_ready seen", "iteration issued"),

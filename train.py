@@ -37,6 +37,9 @@ def main() -> int:
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--log", default=None, help="append JSON lines to this file")
     ap.add_argument("--new-batch-every-step", action="store_true")
+    ap.add_argument("--layers", type=int, default=None, help="override the number of layers")
+    ap.add_argument("--phase-times", action="store_true",
+                    help="log device milliseconds per phase (attention, linear layers, reductions) each step")
     args = ap.parse_args()
 
     import torch
@@ -44,9 +47,10 @@ def main() -> int:
     from ringattention_b200.config import LlamaConfig, TrainConfig
     from ringattention_b200.trainer import Trainer
     from ringattention_b200.utils.metrics import MetricsLogger, step_metrics
-    from ringattention_b200.utils.tracing import nvtx_range
+    from ringattention_b200.utils.tracing import PhaseTimer, nvtx_range, set_phase_timer
 
-    cfg = LlamaConfig.named(args.model, layout=args.layout, remat=args.remat)
+    over = {} if args.layers is None else {"n_layers": args.layers}
+    cfg = LlamaConfig.named(args.model, layout=args.layout, remat=args.remat, **over)
     tc = TrainConfig(model=args.model, mesh=args.mesh, seq_len=args.seq_len, global_batch=args.global_batch,
                      lr=args.lr, steps=args.steps, packed_mean_doc_len=args.packed_mean_doc_len,
                      ckpt_dir=args.ckpt_dir, ckpt_every=args.ckpt_every, resume=args.resume)
@@ -54,6 +58,8 @@ def main() -> int:
     log = MetricsLogger(args.log, rank=tr.rank)
     if args.resume and args.ckpt_dir:
         tr.load_checkpoint(args.ckpt_dir)
+    timer = PhaseTimer() if args.phase_times else None
+    set_phase_timer(timer)
     tokens, targets, seg = tr.make_global_batch()
     for _ in range(args.steps):
         if args.new_batch_every_step:
@@ -63,7 +69,8 @@ def main() -> int:
         with nvtx_range("train_step"):
             loss = tr.train_step(tokens, targets, seg)
         ms = (time.perf_counter() - t0) * 1e3
-        log.log(**step_metrics(tr, ms, loss))
+        extra = {} if timer is None else {"phase_ms": {k: v["ms"] for k, v in timer.summary().items()}}
+        log.log(**step_metrics(tr, ms, loss), **extra)
         if args.ckpt_dir and args.ckpt_every and tr.step_idx % args.ckpt_every == 0:
             tr.save_checkpoint(args.ckpt_dir)
     log.close()
