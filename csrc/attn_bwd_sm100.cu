@@ -67,7 +67,8 @@ struct BwdSmem {
   static constexpr int LSE_OFF = DQ_OFF + 128 * 32 * 4;   // [2 stages][lse2 128 | delta 128]
   static constexpr int SEG_OFF = LSE_OFF + 2 * 256 * 4;   // [2][128] int
   static constexpr int BAR_OFF = SEG_OFF + 2 * 128 * 4;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int VIS_OFF = BAR_OFF + 256;  // [VIS_WORDS] visibility of the q tiles
+  static constexpr int TOTAL = VIS_OFF + VIS_WORDS * 4 + 1024;
 };
 
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes,
@@ -110,15 +111,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
     const long long stride = static_cast<long long>(p.copy_ctas) * BWD_THREADS;
     long long i = static_cast<long long>(blockIdx.x) * BWD_THREADS + threadIdx.x;
-    for (; i + 3 * stride < p.copy_n16; i += 4 * stride) {
-      const uint4 a = p.copy_src[i];
-      const uint4 b = p.copy_src[i + stride];
-      const uint4 c = p.copy_src[i + 2 * stride];
-      const uint4 d = p.copy_src[i + 3 * stride];
-      p.copy_dst[i] = a;
-      p.copy_dst[i + stride] = b;
-      p.copy_dst[i + 2 * stride] = c;
-      p.copy_dst[i + 3 * stride] = d;
+    // 16 loads of 16 bytes in flight per thread (the pull is bound by bytes in flight over NVLink)
+    for (; i + 15 * stride < p.copy_n16; i += 16 * stride) {
+      uint4 r[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) r[u] = p.copy_src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) p.copy_dst[i + u * stride] = r[u];
     }
     for (; i < p.copy_n16; i += stride) p.copy_dst[i] = p.copy_src[i];
     return;
@@ -193,6 +192,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  // which q tiles this kv tile is seen by
+  uint32_t* sVis = reinterpret_cast<uint32_t*>(smem + SM::VIS_OFF);
+  const bool use_vis = nqt <= 32 * VIS_WORDS;
+  if (use_vis)
+    fill_visibility(sVis, nqt, static_cast<int>(threadIdx.x), BWD_THREADS,
+                    [&](int i) { return tile_visible(mk, b, i * 128, k0); });
+  // next q tile at or after i that sees this kv tile, or nqt; every role walks the same mask
+  auto next_vis = [&](int i) -> int {
+    if (use_vis) return vis_next(sVis, i, nqt);
+    for (; i < nqt; ++i)
+      if (tile_visible(mk, b, i * 128, k0)) break;
+    return i;
+  };
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -214,9 +226,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tma_load_4d(sV + s * SM::SLAB_BYTES, &tma_v, kv_full, s * 64, h, k0, b);
       }
       int it = 0;
-      for (int i = 0; i < nqt; ++i) {
+      for (int i = next_vis(0); i < nqt; i = next_vis(i + 1)) {
         const int qi0 = i * 128;
-        if (!tile_visible(mk, b, qi0, k0)) continue;
         const int st = it & 1;
         if (!mbar_wait_relaxed(&q_empty[st], ((it >> 1) & 1) ^ 1u, wc, kTimeoutSmemEmpty)) break;
         mbar_arrive_expect_tx(&q_full[st], SM::TILE_BYTES + 1024);
@@ -264,11 +275,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
         if (leader) umma_commit(s_full);
       };
-      auto next_visible = [&](int i) {
-        for (; i < nqt; ++i)
-          if (tile_visible(mk, b, i * 128, k0)) return i;
-        return nqt;
-      };
+      auto next_visible = [&](int i) { return next_vis(i); };
       bool ok = mbar_wait(kv_full, 0, wc, kTimeoutSmemFull);
       int i = next_visible(0);
       int it = 0;
@@ -361,9 +368,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
     int it = 0;
     bool alive = true;
-    for (int i = 0; i < nqt && alive; ++i) {
+    for (int i = next_vis(0); i < nqt && alive; i = next_vis(i + 1)) {
       const int qi0 = i * 128;
-      if (!tile_visible(mk, b, qi0, k0)) continue;
       const int st = it & 1;
       const uint32_t par = it & 1;
       const bool plain = tile_plain(mk, b, qi0, k0);
@@ -549,9 +555,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     const int row = quad * 32 + lane;  // q row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     int it = 0;
-    for (int i = 0; i < nqt; ++i) {
+    for (int i = next_vis(0); i < nqt; i = next_vis(i + 1)) {
       const int qi0 = i * 128;
-      if (!tile_visible(mk, b, qi0, k0)) continue;
       bool ok = mbar_wait_relaxed(dq_full, it & 1, wc, kTimeoutTmemFull, 32);
       if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();

@@ -50,6 +50,35 @@ __device__ __forceinline__ bool tile_visible(const MaskParams& m, int b, int qi0
   return true;
 }
 
+// ---- per-CTA visibility bitmask ---------------------------------------------------------------------
+// With segment ids every evaluation of tile_visible costs a global-memory round trip. A CTA that walked
+// its tiles one by one spent ~100 us on that walk alone (256 tiles); instead all threads of the CTA
+// evaluate the predicate once, 32 tiles per warp step, into a bitmask in shared memory, and the roles
+// walk the set bits.
+constexpr int VIS_WORDS = 256;  // capacity: 8192 tiles (1M rows); longer launches fall back to the direct walk
+
+// bit t of `words` = pred(t) for t < n (n <= 32 * VIS_WORDS). Call with every thread of the CTA, converged,
+// `nthreads` a multiple of 32; a __syncthreads() must follow before the mask is read.
+template <typename F>
+__device__ __forceinline__ void fill_visibility(uint32_t* words, int n, int tid, int nthreads, F pred) {
+  const int n_pad = (n + 31) & ~31;
+  for (int t = tid; t < n_pad; t += nthreads) {  // a warp's 32 values of t share one word: uniform trip count
+    const bool v = t < n && pred(t);
+    const uint32_t bits = __ballot_sync(0xffffffffu, v);
+    if ((tid & 31) == 0) words[t >> 5] = bits;
+  }
+}
+
+// Smallest set bit at or after t, or n.
+__device__ __forceinline__ int vis_next(const uint32_t* words, int t, int n) {
+  while (t < n) {
+    const uint32_t w = words[t >> 5] >> (t & 31);
+    if (w) return t + __ffs(static_cast<int>(w)) - 1;  // bits at or beyond n are never set
+    t = (t | 31) + 1;
+  }
+  return n;
+}
+
 // True when no entry of the tile needs element-wise masking or bias. With segment ids that is the case
 // when both tiles lie inside one and the same segment (per-tile min == max, equal on both sides), which
 // holds for most tiles of packed documents much longer than a tile.

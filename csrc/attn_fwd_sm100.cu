@@ -56,7 +56,8 @@ struct FwdSmem {
   static constexpr int AUX_OFF = V_OFF + KV_STAGES * KV_TILE_BYTES;  // seg/bias staging
   static constexpr int AUX_BYTES = 2 /*wg*/ * 2 /*buf*/ * 128 * 4 * 2 /*seg+bias*/;
   static constexpr int BAR_OFF = AUX_OFF + AUX_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int VIS_OFF = BAR_OFF + 256;  // [2 q tiles][VIS_WORDS] visibility of the kv tiles
+  static constexpr int TOTAL = VIS_OFF + 2 * VIS_WORDS * 4 + 1024;
 };
 
 template <int D>
@@ -74,15 +75,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
     const long long stride = static_cast<long long>(p.copy_ctas) * FWD_THREADS;
     long long i = static_cast<long long>(blockIdx.x) * FWD_THREADS + threadIdx.x;
-    for (; i + 3 * stride < p.copy_n16; i += 4 * stride) {
-      const uint4 a = p.copy_src[i];
-      const uint4 b = p.copy_src[i + stride];
-      const uint4 c = p.copy_src[i + 2 * stride];
-      const uint4 d = p.copy_src[i + 3 * stride];
-      p.copy_dst[i] = a;
-      p.copy_dst[i + stride] = b;
-      p.copy_dst[i + 2 * stride] = c;
-      p.copy_dst[i + 3 * stride] = d;
+    // 16 loads of 16 bytes in flight per thread: the pull is bound by bytes in flight over the NVLink round
+    // trip; finishing early hands the SM to a compute CTA sooner
+    for (; i + 15 * stride < p.copy_n16; i += 16 * stride) {
+      uint4 r[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) r[u] = p.copy_src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) p.copy_dst[i + u * stride] = r[u];
     }
     for (; i < p.copy_n16; i += stride) p.copy_dst[i] = p.copy_src[i];
     return;
@@ -147,6 +147,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  // which kv tiles each of the two q tiles sees
+  uint32_t* sVis = reinterpret_cast<uint32_t*>(smem + SM::VIS_OFF);
+  const bool use_vis = nk <= 32 * VIS_WORDS;
+  if (use_vis) {
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+      fill_visibility(sVis + w * VIS_WORDS, nk, static_cast<int>(threadIdx.x), FWD_THREADS,
+                      [&](int j) { return tile_visible(mk, b, q0 + w * 128, j * 128); });
+  }
+  // next kv tile at or after j that q tile w sees, or nk
+  auto next_vis = [&](int w, int j) -> int {
+    if (use_vis) return vis_next(sVis + w * VIS_WORDS, j, nk);
+    for (; j < nk; ++j)
+      if (tile_visible(mk, b, q0 + w * 128, j * 128)) break;
+    return j;
+  };
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -166,9 +182,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           tma_load_4d(sQ + w * SM::Q_TILE_BYTES + s * SM::SLAB_BYTES, &tma_q, q_full, s * 64, h,
                       q0 + w * 128, b);
       int it = 0;
-      for (int j = 0; j < nk; ++j) {
+      for (int j = min(next_vis(0, 0), next_vis(1, 0)); j < nk;
+           j = min(next_vis(0, j + 1), next_vis(1, j + 1))) {
         const int k0 = j * 128;
-        if (!(tile_visible(mk, b, q0, k0) || tile_visible(mk, b, q0 + 128, k0))) continue;
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!mbar_wait_relaxed(&k_empty[st], ph ^ 1u, wc, kTimeoutSmemEmpty)) break;
@@ -220,13 +236,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         if (leader) umma_commit(&o_done[w]);
       };
       auto next_visible = [&](int j, bool& v0, bool& v1) {
-        for (; j < nk; ++j) {
-          v0 = tile_visible(mk, b, q0, j * 128);
-          v1 = tile_visible(mk, b, q0 + 128, j * 128);
-          if (v0 || v1) return j;
-        }
-        v0 = v1 = false;
-        return nk;
+        const int a = next_vis(0, j), c = next_vis(1, j);
+        const int jj = min(a, c);
+        v0 = a == jj && jj < nk;
+        v1 = c == jj && jj < nk;
+        return jj;
       };
       bool ok = mbar_wait(q_full, 0, wc, kTimeoutSmemFull);
       bool v0, v1;
@@ -305,10 +319,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     int cnt = 0;
     bool alive = true;
 
-    for (int j = 0; j < nk && alive; ++j) {
+    // every role walks the same visibility mask, so skips stay consistent
+    for (int j = next_vis(w, 0); j < nk && alive; j = next_vis(w, j + 1)) {
       const int k0 = j * 128;
-      // the predicate is evaluated for both tiles by every role so that skips stay consistent
-      if (!tile_visible(mk, b, qi0, k0)) continue;
       const bool plain = tile_plain(mk, b, qi0, k0);
       if (!plain && (mk.seg_k || mk.bias)) {
         const int buf = cnt & 1;

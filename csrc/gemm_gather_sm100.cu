@@ -34,6 +34,8 @@ int launch_gather(const CUtensorMap& ta, const TmaSet& set, const Params& p, con
 // copy CTAs fill). shard_src[s]: the owner's memory for remote shards, null for the own shard.
 // For b_mn = 0, (N, K) are the GEMM dims and W is [N][ldw]; for b_mn = 1 the GEMM computes
 // C[M, N] with reduction length K = number of W rows, and W is [K][ldw] with ldw >= N.
+// copy_ctas == 0: the remote shards are already in `shard_local` from an earlier call whose flag target is
+// passed again; nothing is copied and every CTA computes.
 extern "C" int ra_gemm_bf16_gather(const void* A, void* C, const void* R, int M, int N, int K, long long lda,
                                    long long ldc, long long ldr, int b_mn, int c_fp32, int n_shards,
                                    int my_shard, int shard_rows, long long ldw,
@@ -45,7 +47,7 @@ extern "C" int ra_gemm_bf16_gather(const void* A, void* C, const void* R, int M,
   const int w_rows = b_mn ? K : N;
   if (M <= 0 || N <= 0 || K <= 0 || n_shards < 1 || n_shards > MAX_SHARDS || my_shard < 0 ||
       my_shard >= n_shards || shard_rows % BN || (lda % 8) || (ldw % 8) || (ldc % (c_fp32 ? 4 : 8)) ||
-      static_cast<long long>(shard_rows) * (n_shards - 1) >= w_rows + shard_rows || copy_ctas < 1) {
+      static_cast<long long>(shard_rows) * (n_shards - 1) >= w_rows + shard_rows || copy_ctas < 0) {
     set_error("ra_gemm_bf16_gather: bad shape (shard_rows must be a multiple of 256)");
     return kHostBadArg;
   }

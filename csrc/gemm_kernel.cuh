@@ -96,12 +96,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       long long i = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x;
       const uint4* src = g.src[s];
       uint4* dst = g.dst[s];
-      for (; i + 3 * stride < g.n16[s]; i += 4 * stride) {
-        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
-        dst[i] = a;
-        dst[i + stride] = b;
-        dst[i + 2 * stride] = c;
-        dst[i + 3 * stride] = e;
+      // 16 loads of 16 bytes in flight per thread: the pull is bound by bytes in flight over the NVLink
+      // round trip, so depth per thread matters more than the number of gather CTAs
+      for (; i + 15 * stride < g.n16[s]; i += 16 * stride) {
+        uint4 r[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) r[u] = src[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) dst[i + u * stride] = r[u];
       }
       for (; i < g.n16[s]; i += stride) dst[i] = src[i];
       __threadfence();

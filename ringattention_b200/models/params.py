@@ -36,7 +36,7 @@ def _round_up(x: int, m: int) -> int:
 
 class FlatParams:
     def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
-                 shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 24):
+                 shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 16):
         self.cfg = cfg
         self.device = torch.device(device)
         self.shard_index, self.shard_count = shard
@@ -78,9 +78,21 @@ class FlatParams:
 
             self._symm = SymmBuffer(self.numel_shard * 2, fsdp_group, self.device)
             self.p16_shard = self._symm.local.view(torch.bfloat16)[:self.numel_shard]
-            max_shard = max(_round_up(sr * Kd, 64) for (_, _, Kd, sr) in self.mat.values())
-            self._scratch = torch.empty((f - 1) * max_shard, device=self.device, dtype=torch.bfloat16)
-            self._max_shard = max_shard
+            # Landing area of gathered remote shards: one region per kind of matrix (wqkv, wo, wgu, wd,
+            # lm_head), each holding the f-1 remote shards of ONE matrix of that kind. A matrix stays
+            # resident until another matrix of its kind is gathered, so the chunk loops of the feed-forward
+            # and of the LM head, and the backward right after the recomputation of a layer, reuse the copy.
+            self._kind_off: Dict[str, int] = {}
+            self._kind_size: Dict[str, int] = {}
+            tot = 0
+            for name, (_, _, Kd, sr) in self.mat.items():
+                kind = name.split(".")[-1]
+                if kind not in self._kind_off:
+                    self._kind_off[kind] = tot
+                    self._kind_size[kind] = _round_up(sr * Kd, 64)
+                    tot += (f - 1) * self._kind_size[kind]
+            self._scratch = torch.empty(tot, device=self.device, dtype=torch.bfloat16)
+            self._resident: Dict[str, Tuple[str, int]] = {}   # kind -> (matrix name, flag target of its gather)
             self._flags = torch.zeros(8, dtype=torch.int32, device=self.device)
             self._flag_base = 0
         else:
@@ -179,10 +191,16 @@ class FlatParams:
     def n_params(self) -> int:
         return sum(N * Kd for (_, N, Kd, _) in self.mat.values()) + sum(math.prod(s) for _, s in self.rep.values())
 
+    def invalidate_gathered(self) -> None:
+        """Forget which remote shards are resident (call whenever any rank's weights change)."""
+        if self.shard_count > 1:
+            self._resident.clear()
+
     # ------------------------------------------------------------------ linear layers
     def _gather_call(self, x, name, b_mn: int, out, residual, M, N, Kg):
         off, Nw, Kw, sr = self.mat[name]
         f, me = self.shard_count, self.shard_index
+        kind = name.split(".")[-1]
         local_ptrs, src_ptrs = [], []
         slot = 0
         for s in range(f):
@@ -190,18 +208,24 @@ class FlatParams:
                 local_ptrs.append(self.p16_shard.data_ptr() + off * 2)
                 src_ptrs.append(0)
             else:
-                local_ptrs.append(self._scratch.data_ptr() + slot * self._max_shard * 2)
+                local_ptrs.append(self._scratch.data_ptr() + (self._kind_off[kind] + slot * self._kind_size[kind]) * 2)
                 src_ptrs.append(self._symm.peer_ptrs[s] + off * 2)
                 slot += 1
         LP = (c_vp * f)(*local_ptrs)
         SP = (c_vp * f)(*src_ptrs)
-        self._flag_base += self.gather_ctas
+        hit = self._resident.get(kind)
+        if hit is not None and hit[0] == name:
+            copy_ctas, target = 0, hit[1]          # remote shards already here: all CTAs compute
+        else:
+            self._flag_base += self.gather_ctas
+            copy_ctas, target = self.gather_ctas, self._flag_base
+            self._resident[kind] = (name, target)
         c_fp32 = 1 if out.dtype == torch.float32 else 0
         _lib.call("ra_gemm_bf16_gather", c_vp(x.data_ptr()), c_vp(out.data_ptr()),
                   c_vp(0 if residual is None else residual.data_ptr()), M, N, Kg,
                   c_ll(x.stride(0)), c_ll(out.stride(0)), c_ll(0 if residual is None else residual.stride(0)),
                   b_mn, c_fp32, f, me, sr, c_ll(Kw), LP, SP, c_vp(self._flags.data_ptr()),
-                  ctypes.c_uint(self._flag_base & 0xFFFFFFFF), self.gather_ctas, 8,
+                  ctypes.c_uint(target & 0xFFFFFFFF), copy_ctas, 8,
                   c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr())
         return out
 
@@ -248,6 +272,7 @@ class FlatParams:
                    clip: float, gnorm_sq) -> None:
         common = dict(step=step, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
                       clip=clip, gnorm_sq=gnorm_sq)
+        self.invalidate_gathered()
         K.adamw_(self.p32_s, self.m_s, self.v_s, self.grad_shard(self.shard_index), self.p16_shard,
                  decay_end=self.numel_shard, **common)
         K.adamw_(self.p32_r, self.m_r, self.v_r, self.grad_rep(), self.p16_rep,
@@ -261,6 +286,7 @@ class FlatParams:
     def load_state_dict(self, st: dict) -> None:
         if tuple(st["shard"]) != (self.shard_index, self.shard_count):
             raise ValueError("checkpoint was written with a different fsdp sharding")
+        self.invalidate_gathered()
         for k in ("p32_s", "m_s", "v_s", "p32_r", "m_r", "v_r"):
             getattr(self, k).copy_(st[k])
         self.p16_shard.copy_(self.p32_s)

