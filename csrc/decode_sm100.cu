@@ -299,9 +299,9 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16
 #pragma unroll
   for (int m = 0; m < M; ++m) acc[m] = 0.f;
   const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(warp) * K);
-  for (int c = lane; c < K / 8; c += 32) {
+  auto consume = [&](const uint4& wv, int c) {
     float wf[8];
-    unpack8(wr[c], wf);
+    unpack8(wv, wf);
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float xf[8];
@@ -309,7 +309,17 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
     }
+  };
+  const int n16 = K / 8;
+  int c = lane;
+  for (; c + 96 < n16; c += 128) {  // four 16-byte weight loads in flight per lane
+    const uint4 w0 = wr[c], w1 = wr[c + 32], w2 = wr[c + 64], w3 = wr[c + 96];
+    consume(w0, c);
+    consume(w1, c + 32);
+    consume(w2, c + 64);
+    consume(w3, c + 96);
   }
+  for (; c < n16; c += 32) consume(wr[c], c);
 #pragma unroll
   for (int m = 0; m < M; ++m) {
 #pragma unroll

@@ -46,11 +46,11 @@ def _pad_q(q: torch.Tensor):
 
 
 def default_splits(S: int, B: int, H: int) -> int:
-    """Enough CTAs to fill the GPU many times over (measured on a 128K-row, 32-head shard: 4.57 TB/s with
-    4 CTAs per SM in total, 5.19 TB/s from 14 on), at least 256 cache rows per CTA."""
+    """Many small CTAs: measured on a 128K-row, 32-head shard, 18 splits (4 CTAs per SM in total) gave
+    4.57 TB/s, 74 splits 4.65 (a ragged last wave), 256 splits 5.19. At least 512 cache rows per CTA."""
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    want = max(1, (16 * sms) // max(1, B * H))
-    return max(1, min(want, (S + 255) // 256, 512))
+    want = max(1, (64 * sms) // max(1, B * H))
+    return max(1, min(want, (S + 511) // 512, 512))
 
 
 def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, k_pos0: int = 0,
