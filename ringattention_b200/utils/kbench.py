@@ -61,7 +61,7 @@ def time_launches(fn, warmup: int, iters: int, flush_l2: bool) -> float:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad"])
+    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad", "decode", "small_m_linear"])
     ap.add_argument("--seq", type=int, default=32768)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -116,6 +116,31 @@ def main(argv=None) -> int:
             flops = 10.0 * B * S * S * H * D * frac
             bytes_ = 6.0 * q.numel() * 2 + q.numel() * 4
         res.update(shape=[B, S, H, D], causal=args.causal)
+    elif args.kernel == "decode":
+        # split-KV decode attention over one cache shard: --seq cache rows, one query row per sequence
+        from ..ops import decode as Dk
+
+        B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
+        cache = torch.randn(B, S, 2, H, D, device=dev).bfloat16()
+        q = torch.randn(B, 1, H, D, device=dev).bfloat16()
+        fn = lambda: Dk.decode_partial(q, cache[:, :, 0], cache[:, :, 1], q_pos0=S, k_pos0=0)
+        flops = 4.0 * B * S * H * D
+        bytes_ = 2.0 * B * S * H * D * 2
+        res.update(shape=[B, S, H, D], splits=Dk.default_splits(S, B, H))
+    elif args.kernel == "small_m_linear":
+        # y[M, N] = x[M, K] W[N, K]^T with M <= 8 (decode-time projections): weight bandwidth is the roofline
+        M, N, Kd = min(args.m, 8), args.n, args.k
+        ws = [torch.randn(N, Kd, device=dev).bfloat16() for _ in range(8)]  # rotate so that L2 does not help
+        x = torch.randn(M, Kd, device=dev).bfloat16()
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + 1) % len(ws)
+            K.small_m_linear(x, ws[turn[0]])
+
+        flops = 2.0 * M * N * Kd
+        bytes_ = 2.0 * N * Kd
+        res.update(shape=[M, N, Kd])
     else:
         M, N, Kd = args.m, args.n, args.k
         if args.kernel == "gemm":
