@@ -40,7 +40,18 @@ struct SplitParams {
   long long k_pos0;  // global position of local cache row 0
   const long long* pos_ptr;  // optional: the query position lives on the device (CUDA-graph decode);
                              // then q_pos0 = *pos_ptr and the rows to visit are [0, min(S, *pos_ptr + 1 - k_pos0))
+  // Striped cache (stripe_n > 0, with pos_ptr): the first stripe_base rows of every rank hold the prefilled
+  // context (positions < stripe_len0, all visible); decoded token i = position - stripe_len0 lives on rank
+  // i % stripe_n at row stripe_base + i / stripe_n. No causal rule is needed: every stored row is in the past.
+  int stripe_n, stripe_rank;
+  long long stripe_base, stripe_len0;
 };
+
+// Rows of this rank that hold tokens up to and including position `pos` in the striped layout.
+__device__ __forceinline__ long long striped_rows(long long pos, int n, int rank, long long base, long long len0) {
+  const long long i = pos - len0;
+  return base + (i >= 0 ? (i + n - rank) / n : 0);
+}
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
   const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -84,7 +95,11 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
   int S = p.S, rows_per_split = p.rows_per_split;
   if (p.pos_ptr) {
     q_pos0 = *p.pos_ptr;
-    const long long n = q_pos0 + 1 - p.k_pos0;
+    long long n = q_pos0 + 1 - p.k_pos0;
+    if (p.stripe_n > 0) {
+      n = striped_rows(q_pos0, p.stripe_n, p.stripe_rank, p.stripe_base, p.stripe_len0);
+      q_pos0 = -1;
+    }
     S = static_cast<int>(n < 0 ? 0 : (n > p.S ? p.S : n));
     rows_per_split = (S + p.splits - 1) / p.splits;
     if (rows_per_split < 1) rows_per_split = 1;
@@ -269,8 +284,13 @@ __global__ void decode_merge_kernel(const MergeParams p) {
 // Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to
 // cache row (*pos_ptr - k0) of this rank's (B, S_max, 2, H, D) shard if that position is local.
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ cache,
-                                 const long long* __restrict__ pos_ptr, long long k0, int S_max, int HD) {
-  const long long r = *pos_ptr - k0;
+                                 const long long* __restrict__ pos_ptr, long long k0, int S_max, int HD,
+                                 int stripe_n, int stripe_rank, long long stripe_base, long long stripe_len0) {
+  long long r = *pos_ptr - k0;
+  if (stripe_n > 0) {  // striped layout: token i = pos - len0 belongs to rank i % n, row base + i / n
+    const long long i = *pos_ptr - stripe_len0;
+    r = (i >= 0 && i % stripe_n == stripe_rank) ? stripe_base + i / stripe_n : -1;
+  }
   if (r < 0 || r >= S_max) return;
   const int b = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(b) * 3 + 1) * HD);
@@ -346,6 +366,8 @@ struct RaDecodeArgs {
   float softmax_scale;
   long long q_pos0, k_pos0;
   const long long* pos_ptr;
+  int stripe_n, stripe_rank;
+  long long stripe_base, stripe_len0;
   void* stream;
 };
 
@@ -374,6 +396,8 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
   p.q_pos0 = a->q_pos0;
   p.k_pos0 = a->k_pos0;
   p.pos_ptr = a->pos_ptr;
+  p.stripe_n = a->stripe_n; p.stripe_rank = a->stripe_rank;
+  p.stripe_base = a->stripe_base; p.stripe_len0 = a->stripe_len0;
   dim3 grid(a->splits, a->H, a->B);
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);
 #define RA_LAUNCH_DEC(DD, QQ) decode_splitkv_kernel<DD, QQ><<<grid, THREADS, 0, s>>>(p)
@@ -421,11 +445,13 @@ extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long 
 }
 
 extern "C" int ra_kv_append(const void* qkv, void* cache, const long long* pos_ptr, long long k0, int S_max,
-                            int B, int HD, void* stream) {
+                            int B, int HD, int stripe_n, int stripe_rank, long long stripe_base,
+                            long long stripe_len0, void* stream) {
   using namespace ra::decode;
   if (HD % 8 || B < 1 || !pos_ptr) { set_error("ra_kv_append: bad arguments"); return kHostBadArg; }
   kv_append_kernel<<<B, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(cache), pos_ptr, k0, S_max, HD);
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(cache), pos_ptr, k0, S_max, HD,
+      stripe_n, stripe_rank, stripe_base, stripe_len0);
   return check_launch("kv_append_kernel");
 }
 

@@ -29,6 +29,8 @@ class _DecodeArgs(ctypes.Structure):
         ("softmax_scale", ctypes.c_float),
         ("q_pos0", c_ll), ("k_pos0", c_ll),
         ("pos_ptr", c_vp),
+        ("stripe_n", ctypes.c_int), ("stripe_rank", ctypes.c_int),
+        ("stripe_base", c_ll), ("stripe_len0", c_ll),
         ("stream", c_vp),
     ]
 
@@ -54,7 +56,8 @@ def default_splits(S: int, B: int, H: int) -> int:
 
 
 def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, k_pos0: int = 0,
-                   mask: Optional[torch.Tensor] = None, splits: Optional[int] = None, pos_ptr: int = 0):
+                   mask: Optional[torch.Tensor] = None, splits: Optional[int] = None, pos_ptr: int = 0,
+                   stripe: Optional[tuple] = None):
     """Split-KV pass over this rank's cache rows ``[0, n_valid)``. Returns fp32 partials
     ``(o_part (B*H*QL, splits, D), lse_part (B*H*QL, splits), QL_padded)``."""
     B, QL, H, D = q.shape
@@ -78,6 +81,8 @@ def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, 
     a.softmax_scale = 1.0 / math.sqrt(D)
     a.q_pos0, a.k_pos0 = int(q_pos0), int(k_pos0)
     a.pos_ptr = pos_ptr
+    # striped cache (with pos_ptr): (ranks, rank, prefilled rows per rank, prefilled positions)
+    a.stripe_n, a.stripe_rank, a.stripe_base, a.stripe_len0 = stripe if stripe is not None else (0, 0, 0, 0)
     a.stream = torch.cuda.current_stream().cuda_stream
     _lib.call("ra_decode_splitkv", ctypes.byref(a))
     return o_part, lse_part
@@ -108,7 +113,7 @@ def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None,
 
 def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: Optional[int] = None,
                           q_pos0: int = -1, k_pos0: Optional[int] = None, state: Optional[torch.Tensor] = None,
-                          exchange: int = 0, exchanges_per_step: int = 1):
+                          exchange: int = 0, exchanges_per_step: int = 1, stripe: Optional[tuple] = None):
     """``q (B, q_len<=8, H, D)`` replicated; ``k, v (B, kv_len, H, D)`` local cache shard; boolean
     ``attn_mask`` broadcastable to ``(B, H, q_len, S_total)``, global on the last axis (True =
     attend). Returns ``(B, q_len, H, D)`` in ``v.dtype``, identical on every rank."""
@@ -131,7 +136,7 @@ def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: 
     pos_ptr = 0 if state is None else state.data_ptr()
     step_ptr = 0 if state is None else state.data_ptr() + 8
     o_part, lse_part = decode_partial(qp, k, v, n_valid=n_valid, q_pos0=q_pos0, k_pos0=k_pos0, mask=mask_u8,
-                                      pos_ptr=pos_ptr)
+                                      pos_ptr=pos_ptr, stripe=stripe)
     out = torch.empty(B, QL, H, D, device=q.device, dtype=v.dtype)
     if world == 1:
         merge_partials(o_part, lse_part, H, QL, out=out)

@@ -217,3 +217,21 @@ def test_llama_config_param_count():
     cfg = LlamaConfig.named("llama-7b")
     assert abs(cfg.n_params() - 6.74e9) / 6.74e9 < 0.01
     assert cfg.head_dim == 128
+
+
+def test_phase_timer_is_inert_without_cuda_and_mesh_flops_count_packed_documents():
+    """`phase` regions cost nothing when no timer is installed; the packed-document FLOP count uses only
+    pairs inside a document."""
+    from ringattention_b200.trainer import geometric_segment_ids
+    from ringattention_b200.utils import tracing
+
+    tracing.set_phase_timer(None)
+    with tracing.phase("anything"):
+        x = 1
+    assert x == 1
+    seg = geometric_segment_ids(2, 4096, 512, torch.Generator().manual_seed(0))
+    assert seg.shape == (2, 4096) and bool((seg[:, 1:] >= seg[:, :-1]).all())
+    flat = seg.long() + torch.arange(2)[:, None] * (int(seg.max()) + 1)
+    ln = torch.bincount(flat.flatten()).double()
+    pairs = float((ln * (ln + 1) / 2).sum())
+    assert pairs < 2 * 4096 * 4097 / 2 and pairs >= 2 * 4096

@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _case(B, Sq, Sk, H, D, cbs=0, q_off=0, k_off=0, seg=False, bias=False, pdrop=0.0, prev=False):
+def _case(B, Sq, Sk, H, D, cbs=0, q_off=0, k_off=0, seg=False, bias=False, pdrop=0.0, prev=False, seg_p=0.01):
     from ringattention_b200.ops import _lib, flash, reference as R
 
     torch.manual_seed(0)
@@ -20,7 +20,7 @@ def _case(B, Sq, Sk, H, D, cbs=0, q_off=0, k_off=0, seg=False, bias=False, pdrop
     seg_q = seg_k = bs = None
     if seg:
         tot = max(q_off + Sq, k_off + Sk)
-        ids = torch.cumsum((torch.rand(B, tot, device=dev) < 0.01).int(), dim=1).int()
+        ids = torch.cumsum((torch.rand(B, tot, device=dev) < seg_p).int(), dim=1).int()
         seg_q, seg_k = ids[:, q_pos].contiguous(), ids[:, k_pos].contiguous()
         ms.seg_q, ms.seg_k = seg_q, seg_k
         ms.seg_q_mm, ms.seg_k_mm = flash.seg_tile_minmax(seg_q), flash.seg_tile_minmax(seg_k)
@@ -77,6 +77,14 @@ def test_attention_segments_bias_dropout():
     _case(1, 512, 512, 2, 128, cbs=1, seg=True)
     _case(1, 512, 512, 2, 128, bias=True)
     _case(1, 512, 512, 2, 128, cbs=1, pdrop=0.2)
+
+
+def test_attention_long_documents_take_the_plain_path_inside_a_segment():
+    """Documents several tiles long: tile pairs inside one segment skip the per-column masking, pairs of
+    different segments are skipped through the visibility bitmask, boundary tiles take the masked path."""
+    _case(2, 2048, 2048, 2, 128, cbs=1, seg=True, seg_p=0.002)
+    _case(1, 1536, 2048, 2, 128, cbs=0, seg=True, seg_p=0.003)
+    _case(1, 1024, 1024, 2, 64, cbs=1, seg=True, seg_p=0.004, pdrop=0.1)
 
 
 def test_attention_fully_masked_block_and_carry():
