@@ -36,12 +36,16 @@ int launch_gather(const CUtensorMap& ta, const TmaSet& set, const Params& p, con
 // C[M, N] with reduction length K = number of W rows, and W is [K][ldw] with ldw >= N.
 // copy_ctas == 0: the remote shards are already in `shard_local` from an earlier call whose flag target is
 // passed again; nothing is copied and every CTA computes.
+// pf_dst / pf_src / pf_n16 (all three or none): the copy CTAs pull these ranges (16-byte units, entry
+// `my_shard` ignored) instead of this call's own remote shards, i.e. they prefetch the operand of a later
+// call while this one computes on shards that are already resident; the counters advance as for any gather.
 extern "C" int ra_gemm_bf16_gather(const void* A, void* C, const void* R, int M, int N, int K, long long lda,
                                    long long ldc, long long ldr, int b_mn, int c_fp32, int n_shards,
                                    int my_shard, int shard_rows, long long ldw,
                                    const void* const* shard_local, const void* const* shard_src,
                                    unsigned int* flags, unsigned int flag_target, int copy_ctas,
-                                   int group_m, int* status, void* stream) {
+                                   int group_m, int* status, void* stream, const void* const* pf_dst,
+                                   const void* const* pf_src, const long long* pf_n16) {
   using namespace ra;
   using namespace ra::gemm;
   const int w_rows = b_mn ? K : N;
@@ -84,6 +88,11 @@ extern "C" int ra_gemm_bf16_gather(const void* A, void* C, const void* R, int M,
     g.dst[s] = (s == my_shard) ? nullptr
                                : reinterpret_cast<uint4*>(const_cast<void*>(shard_local[s]));
     g.n16[s] = (s == my_shard) ? 0 : rows * ldw * 2 / 16;
+    if (pf_dst && pf_src && pf_n16 && s != my_shard) {
+      g.src[s] = reinterpret_cast<const uint4*>(pf_src[s]);
+      g.dst[s] = reinterpret_cast<uint4*>(const_cast<void*>(pf_dst[s]));
+      g.n16[s] = pf_n16[s];
+    }
   }
   Params p{C, ldc, M, N, K, c_fp32, R, ldr, group_m > 0 ? group_m : 8, status};
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -163,8 +163,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int kb_rot = (GATHER && B_MN) ? g.my_shard * (g.shard_rows / BK) : 0;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ TMA producer (warp-uniform flow)
+    // All 32 lanes run the loop and poll the barriers; only the elected lane arms the barrier and issues the
+    // loads. With the loop inside an `if (lane == 0)` region every TMA operand had to be moved to a uniform
+    // register first, which matters for dgrad/wgrad (five or six loads per k-block in ~500 cycles).
+    {
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -174,15 +178,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
         tn = (tn + tn_rot) % tiles_n;
         const int m0 = tm * BM, n0 = tn * BN;
+        // Shard of the B rows and the row offset inside it, tracked incrementally: this thread issues
+        // up to five TMA loads per k-block and has ~500 cycles for them, so no division may sit in
+        // the k loop (two of them made the sharded dgrad 60 % slower than the plain one).
+        int kb = kb_rot;
+        int shard = 0, row_in_shard = 0;
+        if (GATHER) {
+          const int w_row = B_MN ? kb * BK : n0;
+          shard = w_row / g.shard_rows;
+          row_in_shard = w_row - shard * g.shard_rows;
+        }
         for (int kbi = 0; kbi < num_kb; ++kbi) {
-          const int kb = (kbi + kb_rot) % num_kb;
           const int k0 = kb * BK;
-          // which shard holds the B rows of this tile / k-block, and the row offset inside it
-          int shard = 0, row_in_shard = 0;
           if (GATHER) {
-            const int w_row = B_MN ? k0 : n0;
-            shard = w_row / g.shard_rows;
-            row_in_shard = w_row - shard * g.shard_rows;
             if (shard != g.my_shard && !((ready_mask >> shard) & 1u)) {
               if (!wait_shard(g, shard, wc)) {
                 ok = false;
@@ -196,27 +204,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&full[stage], STAGE_TX_BYTES);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-          if (A_MN) {
+          if (leader) {
+            mbar_arrive_expect_tx(&full[stage], STAGE_TX_BYTES);
+            if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i)
-              tma_load_2d(a_dst + i * SLAB_BYTES, &tma_a, &full[stage], m0 + 64 * i, k0);
-          } else {
-            tma_load_2d(a_dst, &tma_a, &full[stage], k0, m0);
-          }
-          if (B_MN) {
-            const int kr = GATHER ? row_in_shard : k0;
+              for (int i = 0; i < BM / 64; ++i)
+                tma_load_2d(a_dst + i * SLAB_BYTES, &tma_a, &full[stage], m0 + 64 * i, k0);
+            } else {
+              tma_load_2d(a_dst, &tma_a, &full[stage], k0, m0);
+            }
+            if (B_MN) {
+              const int kr = GATHER ? row_in_shard : k0;
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_2d(b_dst + i * SLAB_BYTES, tma_b, &full[stage], n0 + 64 * i, kr);
-          } else {
-            tma_load_2d(b_dst, tma_b, &full[stage], k0, GATHER ? row_in_shard : n0);
+              for (int i = 0; i < BN / 64; ++i)
+                tma_load_2d(b_dst + i * SLAB_BYTES, tma_b, &full[stage], n0 + 64 * i, kr);
+            } else {
+              tma_load_2d(b_dst, tma_b, &full[stage], k0, GATHER ? row_in_shard : n0);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
+          }
+          if (++kb == num_kb) kb = 0;
+          if (GATHER && B_MN) {  // next k-block: BK rows further, possibly in the next shard, or wrapped
+            row_in_shard += BK;
+            if (kb == 0) {
+              shard = 0;
+              row_in_shard = 0;
+            } else if (row_in_shard >= g.shard_rows) {
+              ++shard;
+              row_in_shard = 0;
+            }
           }
         }
       }

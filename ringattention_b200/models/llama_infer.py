@@ -203,11 +203,20 @@ class LlamaInference:
         self.length += 1
         return self._tok_buf
 
+    def reset(self) -> None:
+        """Forget the cached context (the cache memory is kept). The recorded decode graph is dropped
+        too: it holds the row count and length of the prefilled context as launch constants."""
+        self.length = self.n_rows = self.prefill_len = 0
+        self.state.zero_()
+        self._graph = None
+
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, new_tokens: int, chunk: int = 32768, use_graph: bool = True):
         """Chunked prefill of ``prompt (B, T)`` followed by greedy decoding. Returns the generated
         tokens ``(B, new_tokens)`` and timing: prefill seconds, per-token decode latencies."""
         B, T = prompt.shape
+        if self.length:
+            self.reset()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         logits = None

@@ -34,6 +34,98 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+class GatherSchedule:
+    """Which gathered weight shards are resident, and what to copy during each sharded GEMM call.
+
+    The landing area has two regions per kind of matrix (wqkv, wo, wgu, wd, lm_head). ``plan(name)``
+    is called once per GEMM on matrix ``name`` and returns
+
+    * ``region``: where the call reads the remote shards of ``name``;
+    * ``copy_ctas``/``target``: ``gather_ctas`` and a new flag target when the shards must be pulled by
+      this call (its tiles wait for them), else 0 and the target of the earlier pull;
+    * ``prefetch``: for a call on resident shards, optionally ``(name2, region2, target2)``: the copy
+      CTAs of this call pull matrix ``name2``, the first one the previous step needed after this
+      point that is not resident, into a region no call before it reads.
+
+    Flag targets count copy CTAs cumulatively (every pull adds ``gather_ctas`` to each remote shard's
+    counter). The call sequence of a step is recorded; ``invalidate()`` (after the optimizer step)
+    empties the regions and makes the recorded sequence the prediction for the next step. A wrong
+    prediction only costs a later pull: correctness never depends on it."""
+
+    def __init__(self, kinds, gather_ctas: int, prefetch: bool = True, window: int = 48):
+        self.regions: Dict[str, List[Optional[list]]] = {k: [None, None] for k in kinds}  # [name, target, stamp]
+        self.gather_ctas = gather_ctas
+        self.prefetch = prefetch
+        self.window = window
+        self.flag_base = 0
+        self.stamp = 0
+        self.trace_prev: List[str] = []
+        self.trace_cur: List[str] = []
+        self.trace_ok = True
+        self.stats = {"gathers": 0, "prefetches": 0, "resident_calls": 0}
+
+    @staticmethod
+    def kind(name: str) -> str:
+        return name.split(".")[-1]
+
+    def find(self, name: str) -> int:
+        regs = self.regions[self.kind(name)]
+        for r in (0, 1):
+            if regs[r] is not None and regs[r][0] == name:
+                return r
+        return -1
+
+    def _next_miss(self, i: int, current: str):
+        prev = self.trace_prev
+        if not (self.prefetch and self.trace_ok and i < len(prev)):
+            return None
+        needed = {current}                             # the running call still reads its own shards
+        for j in range(i + 1, min(len(prev), i + 1 + self.window)):
+            nm = prev[j]
+            if self.find(nm) >= 0:
+                needed.add(nm)
+                continue
+            regs = self.regions[self.kind(nm)]
+            free = [r for r in (0, 1) if regs[r] is None or regs[r][0] not in needed]
+            if not free:
+                return None
+            free.sort(key=lambda r: -1 if regs[r] is None else regs[r][2])  # empty first, then least recent
+            return nm, free[0]
+        return None
+
+    def plan(self, name: str) -> dict:
+        regs = self.regions[self.kind(name)]
+        i = len(self.trace_cur)
+        self.trace_cur.append(name)
+        if self.trace_ok and i < len(self.trace_prev) and self.trace_prev[i] != name:
+            self.trace_ok = False                      # this step differs from the last one: no predictions
+        self.stamp += 1
+        r = self.find(name)
+        if r >= 0:
+            regs[r][2] = self.stamp
+            self.stats["resident_calls"] += 1
+            out = {"region": r, "copy_ctas": 0, "target": regs[r][1], "prefetch": None}
+            nxt = self._next_miss(i, name)
+            if nxt is not None:
+                nm2, r2 = nxt
+                self.flag_base += self.gather_ctas
+                self.regions[self.kind(nm2)][r2] = [nm2, self.flag_base, self.stamp]
+                out["copy_ctas"] = self.gather_ctas
+                out["prefetch"] = (nm2, r2, self.flag_base)
+                self.stats["prefetches"] += 1
+            return out
+        r = min((0, 1), key=lambda q: -1 if regs[q] is None else regs[q][2])
+        self.flag_base += self.gather_ctas
+        regs[r] = [name, self.flag_base, self.stamp]
+        self.stats["gathers"] += 1
+        return {"region": r, "copy_ctas": self.gather_ctas, "target": self.flag_base, "prefetch": None}
+
+    def invalidate(self) -> None:
+        for regs in self.regions.values():
+            regs[0] = regs[1] = None
+        self.trace_prev, self.trace_cur, self.trace_ok = self.trace_cur, [], True
+
+
 class FlatParams:
     def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
                  shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 16):
@@ -78,10 +170,12 @@ class FlatParams:
 
             self._symm = SymmBuffer(self.numel_shard * 2, fsdp_group, self.device)
             self.p16_shard = self._symm.local.view(torch.bfloat16)[:self.numel_shard]
-            # Landing area of gathered remote shards: one region per kind of matrix (wqkv, wo, wgu, wd,
+            # Landing area of gathered remote shards: two regions per kind of matrix (wqkv, wo, wgu, wd,
             # lm_head), each holding the f-1 remote shards of ONE matrix of that kind. A matrix stays
-            # resident until another matrix of its kind is gathered, so the chunk loops of the feed-forward
-            # and of the LM head, and the backward right after the recomputation of a layer, reuse the copy.
+            # resident until its region is reused, so the chunk loops of the feed-forward and of the LM
+            # head, and the backward right after the recomputation of a layer, reuse the copy; the
+            # second region lets a call on resident shards prefetch the matrix that the previous step
+            # needed next (the sequence of calls repeats from step to step).
             self._kind_off: Dict[str, int] = {}
             self._kind_size: Dict[str, int] = {}
             tot = 0
@@ -90,11 +184,10 @@ class FlatParams:
                 if kind not in self._kind_off:
                     self._kind_off[kind] = tot
                     self._kind_size[kind] = _round_up(sr * Kd, 64)
-                    tot += (f - 1) * self._kind_size[kind]
+                    tot += 2 * (f - 1) * self._kind_size[kind]
             self._scratch = torch.empty(tot, device=self.device, dtype=torch.bfloat16)
-            self._resident: Dict[str, Tuple[str, int]] = {}   # kind -> (matrix name, flag target of its gather)
+            self.sched = GatherSchedule(self._kind_off.keys(), self.gather_ctas)
             self._flags = torch.zeros(8, dtype=torch.int32, device=self.device)
-            self._flag_base = 0
         else:
             self.p16_shard = torch.empty(self.numel_shard, device=self.device, dtype=torch.bfloat16)
         self.p16_rep = torch.empty(self.numel_rep, device=self.device, dtype=torch.bfloat16)
@@ -194,40 +287,54 @@ class FlatParams:
     def invalidate_gathered(self) -> None:
         """Forget which remote shards are resident (call whenever any rank's weights change)."""
         if self.shard_count > 1:
-            self._resident.clear()
+            self.sched.invalidate()
 
     # ------------------------------------------------------------------ linear layers
-    def _gather_call(self, x, name, b_mn: int, out, residual, M, N, Kg):
+    def _region_ptrs(self, name: str, region: int):
+        """Per shard: local address the GEMM reads, and the owner's address (0 for the own shard)."""
         off, Nw, Kw, sr = self.mat[name]
-        f, me = self.shard_count, self.shard_index
         kind = name.split(".")[-1]
-        local_ptrs, src_ptrs = [], []
+        f, me = self.shard_count, self.shard_index
+        base = self._kind_off[kind] + region * (f - 1) * self._kind_size[kind]
+        local_ptrs, src_ptrs, n16 = [], [], []
         slot = 0
         for s in range(f):
+            rows = max(0, min(sr, Nw - s * sr))
             if s == me:
                 local_ptrs.append(self.p16_shard.data_ptr() + off * 2)
                 src_ptrs.append(0)
+                n16.append(0)
             else:
-                local_ptrs.append(self._scratch.data_ptr() + (self._kind_off[kind] + slot * self._kind_size[kind]) * 2)
+                local_ptrs.append(self._scratch.data_ptr() + (base + slot * self._kind_size[kind]) * 2)
                 src_ptrs.append(self._symm.peer_ptrs[s] + off * 2)
+                n16.append(rows * Kw * 2 // 16)
                 slot += 1
+        return local_ptrs, src_ptrs, n16
+
+    def _gather_call(self, x, name, b_mn: int, out, residual, M, N, Kg):
+        off, Nw, Kw, sr = self.mat[name]
+        f, me = self.shard_count, self.shard_index
+        plan = self.sched.plan(name)
+        PF_D = PF_S = PF_N = None
+        if plan["prefetch"] is not None:
+            nm2, r2, _ = plan["prefetch"]
+            d2, s2, n2 = self._region_ptrs(nm2, r2)
+            PF_D, PF_S, PF_N = (c_vp * f)(*d2), (c_vp * f)(*s2), (c_ll * f)(*n2)
+        local_ptrs, src_ptrs, _ = self._region_ptrs(name, plan["region"])
         LP = (c_vp * f)(*local_ptrs)
         SP = (c_vp * f)(*src_ptrs)
-        hit = self._resident.get(kind)
-        if hit is not None and hit[0] == name:
-            copy_ctas, target = 0, hit[1]          # remote shards already here: all CTAs compute
-        else:
-            self._flag_base += self.gather_ctas
-            copy_ctas, target = self.gather_ctas, self._flag_base
-            self._resident[kind] = (name, target)
         c_fp32 = 1 if out.dtype == torch.float32 else 0
         _lib.call("ra_gemm_bf16_gather", c_vp(x.data_ptr()), c_vp(out.data_ptr()),
                   c_vp(0 if residual is None else residual.data_ptr()), M, N, Kg,
                   c_ll(x.stride(0)), c_ll(out.stride(0)), c_ll(0 if residual is None else residual.stride(0)),
                   b_mn, c_fp32, f, me, sr, c_ll(Kw), LP, SP, c_vp(self._flags.data_ptr()),
-                  ctypes.c_uint(target & 0xFFFFFFFF), copy_ctas, 8,
-                  c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr())
+                  ctypes.c_uint(plan["target"] & 0xFFFFFFFF), plan["copy_ctas"], 8,
+                  c_vp(_lib.status_tensor(self.device).data_ptr()), _lib.stream_ptr(), PF_D, PF_S, PF_N)
         return out
+
+    @property
+    def gather_stats(self) -> dict:
+        return self.sched.stats if self.shard_count > 1 else {}
 
     def lin_fwd(self, x, name: str, out=None, residual=None):
         """``y = x W^T (+ residual)``."""

@@ -91,3 +91,18 @@ def test_graph_replayed_decode_equals_eager_decode():
     assert a._graph is not None and b._graph is None
     assert torch.equal(ga, gb)
     assert int(a.state[0].item()) == a.length == 256 + 12
+
+
+def test_engine_reuse_after_reset_matches_a_fresh_engine():
+    from ringattention_b200.config import LlamaConfig
+    from ringattention_b200.models.llama_infer import LlamaInference
+
+    cfg = LlamaConfig.named("llama-tiny")
+    torch.manual_seed(4)
+    p1 = torch.randint(0, cfg.vocab_size, (1, 256), device="cuda")
+    p2 = torch.randint(0, cfg.vocab_size, (1, 384), device="cuda")
+    eng = LlamaInference(cfg, max_context=1024, batch=1, seed=9)
+    eng.generate(p1, 6, chunk=128)
+    g2, _ = eng.generate(p2, 6, chunk=128)          # resets, re-records the decode graph
+    fresh, _ = LlamaInference(cfg, max_context=1024, batch=1, seed=9).generate(p2, 6, chunk=128)
+    assert torch.equal(g2, fresh) and eng.length == 384 + 6

@@ -70,6 +70,8 @@ def main() -> int:
             loss = tr.train_step(tokens, targets, seg)
         ms = (time.perf_counter() - t0) * 1e3
         extra = {} if timer is None else {"phase_ms": {k: v["ms"] for k, v in timer.summary().items()}}
+        if timer is not None and getattr(tr.model.params, "shard_count", 1) > 1:
+            extra["gather"] = dict(tr.model.params.gather_stats)  # cumulative: gathers, prefetches, resident calls
         log.log(**step_metrics(tr, ms, loss), **extra)
         if args.ckpt_dir and args.ckpt_every and tr.step_idx % args.ckpt_every == 0:
             tr.save_checkpoint(args.ckpt_dir)
