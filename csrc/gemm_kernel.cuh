@@ -160,7 +160,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   // with a sharded B the tile order (B along N) or the k-block order (B along K) is rotated so
   // that work touching only local rows comes first
   const int tn_rot = (GATHER && !B_MN) ? g.my_shard * (g.shard_rows / BN) : 0;
-  const int kb_rot = (GATHER && B_MN) ? g.my_shard * (g.shard_rows / BK) : 0;
+  // (a trailing shard can be empty: its first k-block index then equals num_kb, hence the modulo)
+  const int kb_rot = (GATHER && B_MN) ? (g.my_shard * (g.shard_rows / BK)) % num_kb : 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (warp-uniform flow)
