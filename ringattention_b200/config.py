@@ -17,6 +17,9 @@ import torch
 # (ringattention_jax.py:130,334); only the two below have an effect here.
 POLICY_NOTHING_SAVEABLE = "nothing_saveable"
 POLICY_EVERYTHING_SAVEABLE = "everything_saveable"
+# Model-level extension: recompute a layer in the backward pass except its attention, whose output and
+# log-sum-exp are kept (0.5 GB per layer at 64K tokens x 4096). Not one of the reference's policies.
+POLICY_SAVE_ATTENTION = "save_attention"
 
 _REFERENCE_KEYS = (
     "causal_block_size", "query_chunk_size", "key_chunk_size", "deterministic", "dropout_rng",

@@ -9,7 +9,8 @@ optimizer, the gradient all-reduce and checkpoints are single operations.
 
 Remat policy ``nothing_saveable`` (ringattention_jax.py:334) keeps only the layer inputs and
 recomputes each layer, attention included, in the backward pass. ``everything_saveable`` keeps the
-per-layer activations that backward needs.
+per-layer activations that backward needs. ``save_attention`` (an extension) recomputes the layer
+but keeps the attention output and log-sum-exp, so the ring forward runs once per layer and step.
 """
 from __future__ import annotations
 
@@ -18,7 +19,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..config import POLICY_NOTHING_SAVEABLE, BlockwiseKwargs, LlamaConfig
+from ..config import POLICY_NOTHING_SAVEABLE, POLICY_SAVE_ATTENTION, BlockwiseKwargs, LlamaConfig
 from ..ops import attention as A
 from ..ops import kernels as K
 from ..ops.flash import Positions
@@ -65,7 +66,9 @@ class LlamaModel:
                            total_tokens=total_tokens if total_tokens is not None else B * S_local * world)
 
     # ------------------------------------------------------------------ layer forward
-    def _attn_block_fwd(self, l: int, x: torch.Tensor, ctx: StepContext):
+    def _attn_block_fwd(self, l: int, x: torch.Tensor, ctx: StepContext, kept_attn=None):
+        """``kept_attn = (attn, lse)`` from the forward pass skips the ring forward (recomputation under
+        the ``save_attention`` policy)."""
         cfg, P = self.cfg, self.params
         B, S, H, D, d = ctx.B, ctx.S, self.H, self.D, cfg.d_model
         h1, rstd1 = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
@@ -74,8 +77,11 @@ class LlamaModel:
         qk = qkv.view(B, S, 3 * H, D)[:, :, :2 * H]  # q heads then k heads
         K.rope_(qk, ctx.positions, cfg.rope_theta)
         q, k, v = qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]
-        with phase("attn_fwd"):
-            attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
+        if kept_attn is not None:
+            attn, lse = kept_attn
+        else:
+            with phase("attn_fwd"):
+                attn, lse = A.ring_forward(q, k, v, ctx.plan, ctx.symm_ring)
         x2 = P.lin_fwd(attn.view(B * S, d), f"l{l}.wo", residual=x)
         return x2, (h1, rstd1, qkv, attn, lse)
 
@@ -97,6 +103,8 @@ class LlamaModel:
         x3 = self._ffn_fwd(l, x2, h2)
         if keep:
             return x3, saved + (x2, h2, rstd2)
+        if self.cfg.remat == POLICY_SAVE_ATTENTION:
+            return x3, (saved[3], saved[4])  # attention output and log-sum-exp only
         return x3, None
 
     # ------------------------------------------------------------------ layer backward
@@ -104,8 +112,8 @@ class LlamaModel:
         cfg, P = self.cfg, self.params
         B, S, H, D, d = ctx.B, ctx.S, self.H, self.D, cfg.d_model
         M = B * S
-        if saved is None:  # nothing_saveable: recompute the layer up to the FFN input
-            x2, s = self._attn_block_fwd(l, x, ctx)
+        if saved is None or len(saved) == 2:  # recompute the layer up to the FFN input (attention kept or not)
+            x2, s = self._attn_block_fwd(l, x, ctx, kept_attn=saved)
             h2, rstd2 = K.rmsnorm_fwd(x2, P.w(f"l{l}.n2"), cfg.rms_eps)
             saved = s + (x2, h2, rstd2)
         h1, rstd1, qkv, attn, lse, x2, h2, rstd2 = saved
@@ -174,7 +182,7 @@ class LlamaModel:
         P.ensure_grads()
         tok = tokens.reshape(-1).contiguous()
         x = K.embedding_fwd(tok, P.w("embed"))
-        keep = cfg.remat != POLICY_NOTHING_SAVEABLE
+        keep = cfg.remat not in (POLICY_NOTHING_SAVEABLE, POLICY_SAVE_ATTENTION)
         layer_inputs: List[torch.Tensor] = []
         saved_all: List[object] = []
         for l in range(cfg.n_layers):

@@ -30,7 +30,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--layout", default="contiguous", choices=["contiguous", "zigzag"])
-    ap.add_argument("--remat", default="nothing_saveable", choices=["nothing_saveable", "everything_saveable"])
+    ap.add_argument("--remat", default="nothing_saveable", choices=["nothing_saveable", "everything_saveable", "save_attention"])
     ap.add_argument("--packed-mean-doc-len", type=int, default=0)
     ap.add_argument("--ckpt-dir", default=None)
     ap.add_argument("--ckpt-every", type=int, default=0)
