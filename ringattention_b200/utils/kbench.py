@@ -61,7 +61,7 @@ def time_launches(fn, warmup: int, iters: int, flush_l2: bool) -> float:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad", "decode", "small_m_linear"])
+    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad", "decode", "small_m_linear", "sdpa_fwd", "sdpa_bwd"])
     ap.add_argument("--seq", type=int, default=32768)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -116,6 +116,26 @@ def main(argv=None) -> int:
             flops = 10.0 * B * S * S * H * D * frac
             bytes_ = 6.0 * q.numel() * 2 + q.numel() * 4
         res.update(shape=[B, S, H, D], causal=args.causal)
+    elif args.kernel.startswith("sdpa"):
+        # library comparison: torch.nn.functional.scaled_dot_product_attention (cuDNN / flash backend chosen
+        # by torch) on the same shape; not used by the framework
+        import torch.nn.functional as F
+
+        B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
+        q, k, v = [torch.randn(B, S, H, D, device=dev).bfloat16().transpose(1, 2).requires_grad_(True) for _ in range(3)]
+        frac = 0.5 if args.causal else 1.0
+        if args.kernel == "sdpa_fwd":
+            def fn():
+                with torch.no_grad():
+                    F.scaled_dot_product_attention(q, k, v, is_causal=bool(args.causal))
+            flops = 4.0 * B * S * S * H * D * frac
+        else:
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=bool(args.causal))
+            do = torch.randn_like(o)
+            fn = lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+            flops = 10.0 * B * S * S * H * D * frac
+        bytes_ = 4.0 * q.numel() * 2
+        res.update(shape=[B, S, H, D], causal=args.causal, library=True)
     elif args.kernel == "decode":
         # split-KV decode attention over one cache shard: --seq cache rows, one query row per sequence
         from ..ops import decode as Dk
