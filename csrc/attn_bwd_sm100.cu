@@ -250,7 +250,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, 0, 1);
-      constexpr uint32_t idesc_dk = make_idesc_bf16(128, D, 0, 1);
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
       constexpr uint32_t SLAB = SM::SLAB_BYTES;
       // descriptor bases: *_k = K-major view (rows of 128 B along the reduction dim),
@@ -260,7 +259,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const uint64_t v_k = make_smem_desc(smem_u32(sV), 16, 1024);
       const uint64_t do_k = make_smem_desc(smem_u32(sDO), 16, 1024);
       const uint64_t do_mn = make_smem_desc(smem_u32(sDO), SLAB, 1024);
-      const uint64_t ds_k = make_smem_desc(smem_u32(sDS), 16, 1024);
       const uint64_t ds_mn = make_smem_desc(smem_u32(sDS), SLAB, 1024);
       const uint64_t q_k[2] = {make_smem_desc(smem_u32(sQ), 16, 1024),
                                make_smem_desc(smem_u32(sQ + SM::TILE_BYTES), 16, 1024)};
@@ -327,10 +325,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         trace_event(p.trace, tr && leader, 0, it, 2);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;
+          const uint32_t a_col = tDP + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);  // dS^T in TMEM, laid out like P^T
           if (leader)
-            umma_ss(tDK, desc_advance(ds_k, a_off), desc_advance(q_mn[st], kk * 2048), idesc_dk,
-                    (it != 0 || kk != 0) ? 1u : 0u);
+            umma_ts(tDK, a_col, desc_advance(q_mn[st], kk * 2048), idesc_dv, (it != 0 || kk != 0) ? 1u : 0u);
         }
         if (leader) umma_commit(&q_empty[st]);
 #pragma unroll
@@ -470,6 +467,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t dp[32];
+        uint32_t dsw[16];
         tmem_ld_x32(tDP + lane_base + half * 64 + c * 32, dp);
         tmem_ld_wait();
 #pragma unroll
@@ -491,8 +489,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           v.w = pack_bf16x2(a6, a7);
           const int chunk = c * 4 + g;  // 16-byte chunk inside the 128-byte row
           *reinterpret_cast<uint4*>(ds_row + ((chunk ^ swz) << 4)) = v;
+          dsw[4 * g] = v.x;
+          dsw[4 * g + 1] = v.y;
+          dsw[4 * g + 2] = v.z;
+          dsw[4 * g + 3] = v.w;
         }
+        // dS^T also goes back over the dP^T columns this thread has already read, packed like P^T, and feeds
+        // the dK MMA from TMEM: one 32 KB shared-memory operand read less per iteration
+        tmem_st_x16(tDP + lane_base + half * 64 + c * 16, dsw);
       }
+      tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(ds_ready);
