@@ -146,6 +146,21 @@ class DeviceMesh:
     def axis(self, name: str) -> AxisContext:
         return self._axes[name]
 
+    def replica_group(self, name: str):
+        """Process group of the ranks that share this rank's coordinate on axis ``name`` (every
+        combination of the other axes); ``None`` when that is this rank alone or there is no process
+        group. Collective: every rank of the job must call it, in the same order."""
+        if self.world_size == 1 or self.size(name) == self.world_size:
+            return None
+        ai = self.AXES.index(name)
+        mine = None
+        for v in range(self.config.shape()[ai]):
+            ranks = [r for r in range(self.world_size) if self.rank_to_coords(r)[ai] == v]
+            g = dist.new_group(ranks)
+            if self.coords[ai] == v:
+                mine = g
+        return mine
+
     def size(self, name: str) -> int:
         return self._axes[name].size
 

@@ -19,6 +19,7 @@ from .models.params import FlatParams
 from .ops import _lib
 from .ops import kernels as K
 from .ops.reference import shard_positions
+from .parallel import gradsync
 from .parallel.mesh import DeviceMesh
 from .utils.tracing import phase
 
@@ -111,6 +112,10 @@ class Trainer:
 
             self.symm_ring = SymmRing(self.mesh.axis("sp").group, self.device)
             self.mesh.axis("sp").symm_ring = self.symm_ring
+        # ranks that hold the same parameter shard (same fsdp coordinate): they all-reduce its gradient
+        self._replica_group = None
+        if self.fsdp > 1 and not standalone:
+            self._replica_group = self.mesh.replica_group("fsdp")
         self.step_idx = 0
         self._sync_token = torch.zeros(1, device=self.device)
         self.gnorm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
@@ -179,9 +184,12 @@ class Trainer:
         return loss_sum / max(1, ctx.total_tokens)
 
     def _all_reduce_grads(self, bucket: int = 1 << 28) -> None:
-        g = self.model.params.g32
-        for s0 in range(0, g.numel(), bucket):
-            dist.all_reduce(g[s0:s0 + bucket])
+        """Sum the gradients over the job: all-reduce, or with fsdp > 1 a reduce-scatter over the fsdp
+        axis plus an all-reduce of the owned shard over the ranks sharing the fsdp coordinate."""
+        P = self.model.params
+        gradsync.reduce_gradients(P.g32, P.numel_shard, P.shard_count, P.shard_index,
+                                  self.mesh.axis("fsdp").group if self.fsdp > 1 else None,
+                                  self._replica_group, bucket)
 
     def optimizer_step(self) -> None:
         P, tc = self.model.params, self.tc
@@ -189,7 +197,13 @@ class Trainer:
         clip = float(tc.grad_clip)
         if clip > 0:
             self.gnorm_sq.zero_()
-            K.sumsq(P.g32, self.gnorm_sq)
+            if self.fsdp == 1:
+                K.sumsq(P.g32, self.gnorm_sq)
+            else:  # only the owned shard and the replicated tail hold full sums
+                tail = torch.zeros_like(self.gnorm_sq)
+                K.sumsq(P.grad_shard(P.shard_index), self.gnorm_sq)
+                K.sumsq(P.grad_rep(), tail)
+                self.gnorm_sq.copy_(gradsync.global_sumsq(self.gnorm_sq, tail, self.mesh.axis("fsdp").group))
         P.adamw_step(self.step_idx, tc.lr, tc.beta1, tc.beta2, tc.eps, tc.weight_decay, clip,
                      self.gnorm_sq if clip > 0 else None)
         if self.fsdp > 1:
