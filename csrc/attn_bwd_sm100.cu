@@ -376,10 +376,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
               (qi0 + sm_tid) < mk.Sq ? mk.seg_q[static_cast<long long>(b) * mk.Sq + qi0 + sm_tid] : -2;
         named_bar_sync(1, 256);
       }
-      if (!mbar_wait(&q_full[st], (it >> 1) & 1, wc, kTimeoutSmemFull)) { alive = false; break; }
+      // a wait that gives up must end the loop for the whole warp: the TMEM loads and stores below are
+      // warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(&q_full[st], (it >> 1) & 1, wc, kTimeoutSmemFull))) { alive = false; break; }
       const float4* nl4 = reinterpret_cast<const float4*>(sLse + st * 256 + half * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(sLse + st * 256 + 128 + half * 64);
-      if (!mbar_wait(s_full, par, wc, kTimeoutTmemFull)) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, par, wc, kTimeoutTmemFull))) { alive = false; break; }
       tc_fence_after();
       trace_event(p.trace, tr && sm_tid == 0, 1, it, 0);
 
@@ -459,9 +461,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       mbar_arrive(p_ready);
       trace_event(p.trace, tr && sm_tid == 0, 1, it, 1);
 
-      if (!mbar_wait(dp_full, par, wc, kTimeoutTmemFull)) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(dp_full, par, wc, kTimeoutTmemFull))) { alive = false; break; }
       // the dS buffer is still being read by the previous dK/dQ MMAs until dq_full fires
-      if (it > 0 && !mbar_wait(dq_full, (it - 1) & 1, wc, kTimeoutTmemFull)) { alive = false; break; }
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_full, (it - 1) & 1, wc, kTimeoutTmemFull))) { alive = false; break; }
       tc_fence_after();
       trace_event(p.trace, tr && sm_tid == 0, 1, it, 2);
 #pragma unroll

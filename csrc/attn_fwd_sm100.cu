@@ -334,10 +334,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
               kc < mk.Sk ? mk.bias[b * mk.bias_stride_b + h * mk.bias_stride_h + kc] * kLog2e : 0.f;
         named_bar_sync(1 + w, 128);
       }
-      if (!mbar_wait(&s_full[w], cnt & 1, wc, kTimeoutTmemFull)) {
-        alive = false;
-        break;
-      }
+      // A wait that gives up must end the loop for the whole warp (the TMEM loads and stores are
+      // warp-collective). The lanes agree on that in the vote of the rescale check below, which exists
+      // anyway; until then every lane carries on (a lane that gave up merely loads a stale tile).
+      const bool s_ok = mbar_wait(&s_full[w], cnt & 1, wc, kTimeoutTmemFull);
       tc_fence_after();
       uint32_t sr[128];
 #pragma unroll
@@ -407,12 +407,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 
       // ---- online softmax with lazy rescale of the accumulator
       const float m_new = fmaxf(m_ref, mx);
+      // also true when m_ref is -inf and m_new is finite
+      const bool need = cnt != 0 && m_new > m_ref + 8.0f;
+      const bool rare = __any_sync(0xffffffffu, need || !s_ok);
+      if (rare && __any_sync(0xffffffffu, !s_ok)) {
+        alive = false;
+        break;
+      }
       if (cnt == 0) {
         m_ref = m_new;
       } else {
-        const bool need = m_new > m_ref + 8.0f;  // also true when m_ref is -inf and m_new is finite
-        if (__any_sync(0xffffffffu, need)) {
-          if (!mbar_wait(&o_done[w], (cnt - 1) & 1, wc, kTimeoutTmemFull)) {
+        if (rare) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&o_done[w], (cnt - 1) & 1, wc, kTimeoutTmemFull))) {
             alive = false;
             break;
           }
