@@ -5,7 +5,8 @@ The kernels of one rank run in stream order; different ranks run concurrently an
 flag barrier. A schedule is safe if no rank ever writes a buffer while another rank may still be
 reading or writing it. :func:`check_schedule` explores *every* interleaving of N ranks that the
 barriers allow (each kernel is a begin and an end event with read and write sets) and reports the
-first conflict. The programs below mirror ``parallel/symm.py`` and ``ops/decode.py``; the tests run
+first conflict. The programs below mirror ``parallel/symm.py``, ``ops/decode.py`` and the sharded
+weights of ``models/params.py``; the tests run
 them for small N and several consecutive calls, and also check that removing a barrier or the
 double buffering is detected.
 """
@@ -83,6 +84,25 @@ def decode_program(rank: int, n: int, calls: int, double_buffer: bool = True) ->
         ops.append(kernel(f"push{c}", writes=[("inbox", r, slot, rank) for r in range(n)]))
         ops.append(BARRIER)
         ops.append(kernel(f"merge{c}", reads=[("inbox", rank, slot, s) for s in range(n)]))
+    return ops
+
+
+def fsdp_program(rank: int, n: int, steps: int, gemms: int = 3, sync_after_update: bool = True,
+                 reduce_before_update: bool = True) -> List[Op]:
+    """Training steps with row-sharded weights (``models/params.py``): the GEMMs of a step read every
+    peer's bf16 shard in place (copy CTAs) and write the local landing area; the gradient reduction
+    is a collective every rank enters after its own backward; the optimizer then rewrites the own
+    shard; a small collective after the update keeps peers from starting the next step early."""
+    ops: List[Op] = []
+    for t in range(steps):
+        for g in range(gemms):
+            ops.append(kernel(f"gemm{t}.{g}", reads=[("shard", s) for s in range(n)] + [("landing", rank)],
+                              writes=[("landing", rank)]))
+        if reduce_before_update:
+            ops.append(BARRIER)   # gradient reduce-scatter / all-reduce
+        ops.append(kernel(f"adamw{t}", writes=[("shard", rank)]))
+        if sync_after_update:
+            ops.append(BARRIER)   # sync token
     return ops
 
 

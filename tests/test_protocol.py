@@ -41,3 +41,19 @@ def test_decode_inbox_is_race_free(n):
 def test_decode_single_buffer_races():
     progs = [P.decode_program(r, 2, calls=2, double_buffer=False) for r in range(2)]
     assert P.check_schedule(progs) is not None
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_fsdp_weight_gather_is_race_free(n):
+    from ringattention_b200.parallel.protocol import check_schedule, fsdp_program
+
+    assert check_schedule([fsdp_program(r, n, steps=2) for r in range(n)]) is None
+
+
+def test_fsdp_needs_the_collectives_around_the_update():
+    from ringattention_b200.parallel.protocol import check_schedule, fsdp_program
+
+    # without the sync after the optimizer a peer's next step may read a shard that is being rewritten
+    assert check_schedule([fsdp_program(r, 2, steps=2, sync_after_update=False) for r in range(2)]) is not None
+    # without the gradient collective a rank may rewrite its shard while a slower peer still reads it
+    assert check_schedule([fsdp_program(r, 2, steps=1, reduce_before_update=False) for r in range(2)]) is not None
