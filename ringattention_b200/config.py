@@ -8,7 +8,7 @@ parameters of its blockwise functions (ringattention/ringattention_jax.py:99-100
 from __future__ import annotations
 
 import dataclasses
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Mapping, Optional
 
 import torch

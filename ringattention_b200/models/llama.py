@@ -15,7 +15,7 @@ but keeps the attention output and log-sum-exp, so the ring forward runs once pe
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional
 
 import torch
 

@@ -18,7 +18,6 @@ of the chunk being prefilled are masked causally at their true positions.
 """
 from __future__ import annotations
 
-import math
 import time
 from typing import List, Optional
 
@@ -26,7 +25,6 @@ import torch
 import torch.distributed as dist
 
 from ..config import LlamaConfig
-from ..ops import attention as A
 from ..ops import decode as Dk
 from ..ops import flash
 from ..ops import kernels as K

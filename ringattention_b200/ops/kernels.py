@@ -6,7 +6,6 @@ fall back to PyTorch math. Shapes follow the LLaMA driver: activations are ``(ro
 from __future__ import annotations
 
 import ctypes
-import math
 from typing import Optional
 
 import torch

@@ -12,8 +12,6 @@ backend (NCCL, gloo), in buckets so that no single collective exceeds ``bucket``
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 import torch.distributed as dist
 

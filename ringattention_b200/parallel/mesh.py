@@ -10,7 +10,7 @@ axis_name="sp")`` looks the ring up in that registry.
 from __future__ import annotations
 
 import threading
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, Optional
 
 import torch

@@ -13,7 +13,7 @@ double buffering is detected.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, FrozenSet, List, Optional, Tuple
+from typing import FrozenSet, List, Optional, Tuple
 
 
 @dataclass(frozen=True)

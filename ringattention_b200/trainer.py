@@ -6,8 +6,6 @@ from __future__ import annotations
 
 import json
 import os
-import time
-from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import torch
