@@ -8,7 +8,8 @@ gradients (full size), one saved layer input per layer (``nothing_saveable``), t
 layer being recomputed and differentiated, the chunked FFN / LM-head temporaries and, for sp > 1,
 the symmetric KV slots, the two local slabs, the fp32 dK/dV accumulator and the fp32 output carry.
 Activation memory is linear in the tokens per GPU, so the maximum context grows linearly with the
-number of GPUs on the sp axis (the reference's claim, README.md:5).
+number of GPUs on the sp axis (the reference's claim, README.md:5). ``inference_max_context`` does the
+same for the striped KV cache of the inference engine.
 """
 from __future__ import annotations
 
@@ -25,7 +26,9 @@ def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int 
     n_rep = cfg.vocab_size * cfg.d_model + (2 * cfg.n_layers + 1) * cfg.d_model
     T = tokens_per_gpu * batch
     d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
-    weights = (n_mat / fsdp + n_rep) * 2 + (0 if fsdp == 1 else (fsdp - 1) / fsdp * 2 * max(3 * d * d, 2 * F * d, V * d))
+    # sharded weights: own shard + the landing area of gathered shards (two regions per kind of matrix)
+    landing = 0 if fsdp == 1 else 2 * (fsdp - 1) / fsdp * 2 * (4 * d * d + 3 * F * d + V * d)
+    weights = (n_mat / fsdp + n_rep) * 2 + landing
     optimizer = (n_mat / fsdp + n_rep) * 12
     grads = (n_mat + n_rep) * 4
     saved = cfg.n_layers * T * d * 2
@@ -54,11 +57,28 @@ def max_context(cfg: LlamaConfig, gpus: int, hbm_bytes: float = 178 * GiB, fsdp:
     return lo * sp
 
 
+def inference_max_context(cfg: LlamaConfig, gpus: int, batch: int = 1, chunk: int = 32768,
+                          hbm_bytes: float = 178 * GiB, reserve: float = 0.06) -> int:
+    """Longest context per sequence (multiple of 128 * gpus) whose striped KV cache fits beside the
+    replicated bf16 weights and the working set of one prefill chunk (``models/llama_infer.py``)."""
+    d, F, V = cfg.d_model, cfg.d_ff, cfg.vocab_size
+    n_par = cfg.n_layers * (4 * d * d + 3 * d * F) + 2 * V * d
+    t = chunk // gpus
+    # per chunk: gathered queries + fp32 partials and their exchange buffers (x3), local qkv, ffn chunk
+    work = batch * (chunk * d * (2 + 3 * 4) + t * d * 2 * 8 + min(cfg.ffn_chunk_size, t) * 3 * F * 2)
+    free = hbm_bytes * (1 - reserve) - n_par * 2 - work
+    per_token = 2 * d * 2 * cfg.n_layers / gpus * batch          # K and V, bf16, all layers, this GPU's share
+    ctx = int(free / per_token)
+    return max(0, ctx // (128 * gpus) * (128 * gpus))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     ap.add_argument("--model", default="llama-7b")
     ap.add_argument("--gpus", type=int, nargs="+", default=[1, 2, 4, 8])
     ap.add_argument("--fsdp", type=int, default=1)
+    ap.add_argument("--inference-batch", type=int, default=0,
+                    help="also print the longest inference context for this batch size")
     args = ap.parse_args(argv)
     cfg = LlamaConfig.named(args.model)
     for g in args.gpus:
@@ -66,6 +86,9 @@ def main(argv=None) -> int:
         b = bytes_per_gpu(cfg, ctx // max(1, g // args.fsdp), g // args.fsdp, args.fsdp)
         print(json.dumps({"gpus": g, "fsdp": args.fsdp, "max_context_tokens": ctx,
                           "gib_per_gpu": {k: round(v / GiB, 1) for k, v in b.items()}}))
+        if args.inference_batch:
+            print(json.dumps({"gpus": g, "inference_batch": args.inference_batch,
+                              "max_inference_context_tokens": inference_max_context(cfg, g, args.inference_batch)}))
     return 0
 
 

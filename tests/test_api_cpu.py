@@ -235,3 +235,18 @@ def test_phase_timer_is_inert_without_cuda_and_mesh_flops_count_packed_documents
     ln = torch.bincount(flat.flatten()).double()
     pairs = float((ln * (ln + 1) / 2).sum())
     assert pairs < 2 * 4096 * 4097 / 2 and pairs >= 2 * 4096
+
+
+def test_memory_planner_scales_linearly_with_the_ring_size():
+    from ringattention_b200.config import LlamaConfig
+    from ringattention_b200.utils import memory as M
+
+    cfg = LlamaConfig.named("llama-7b")
+    ctx = {n: M.max_context(cfg, n) for n in (1, 2, 4, 8)}
+    assert 140_000 < ctx[1] < 160_000
+    assert ctx[4] == 2 * ctx[2] and ctx[8] == 4 * ctx[2]        # same tokens per GPU from 2 GPUs on
+    assert M.bytes_per_gpu(cfg, 65536, sp=8)["total"] < 178 * M.GiB
+    inf = {n: M.inference_max_context(cfg, n) for n in (1, 8)}
+    assert inf[8] > 1_048_576 and 7 * inf[1] < inf[8] < 9 * inf[1]
+    # sharding the weights over fsdp frees optimizer memory
+    assert M.bytes_per_gpu(cfg, 32768, sp=4, fsdp=2)["optimizer"] < M.bytes_per_gpu(cfg, 32768, sp=4)["optimizer"]
