@@ -12,6 +12,13 @@ Rank 0 prints one JSON line. ``value`` is whole-job tokens/s of the device-timed
 same metric through ``Trainer.train_step`` including, every step, the pinned host->device copy of
 the token shard and the device->host read of the loss. ``--impl reference`` reports whether the
 unmodified reference can run here.
+
+The whole run is held to ``--time-budget`` seconds of wall clock (default 600; 0 = no limit). A 512K-token
+step on 8 GPUs takes most of a minute, so the requested counts may not fit: the first warm-up step is
+timed and the counts are cut in this order: warm-up down to 3, end-to-end steps down to 2, timed steps down
+to 3, and only then warm-up below 3 (never below 1). The JSON line reports the counts that actually ran in
+``steps`` / ``warmup`` / ``e2e.steps`` and the requested ones in ``steps_requested`` / ``warmup_requested``.
+Every step trains on a different batch (a small pool of synthetic batches is cycled).
 """
 from __future__ import annotations
 
@@ -23,6 +30,8 @@ import subprocess
 import sys
 import threading
 import time
+
+T_START = time.perf_counter()
 
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -45,7 +54,35 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override layer count (debug only; "
                     "a run with this flag is not the headline config)")
     ap.add_argument("--packed-mean-doc-len", type=int, default=0)
+    ap.add_argument("--time-budget", type=float, default=600.0,
+                    help="wall-clock seconds for the whole run, counted from process start (0 = no limit)")
     return ap.parse_args()
+
+
+def plan_counts(warmup_req: int, steps_req: int, warmup_done: int, step_s: float, remaining_s: float):
+    """How many more warm-up steps, timed steps and end-to-end steps fit into ``remaining_s`` seconds at
+    ``step_s`` seconds per step. Floors: 3 timed steps, 2 end-to-end steps, 3 warm-up steps in total while
+    they fit (1 otherwise); what is left over goes to the timed steps, then to the end-to-end steps (at most
+    as many as timed steps), then to the warm-up. Returns ``(more_warmup, timed, e2e)``."""
+    steps_req = max(1, steps_req)
+    k_min, e_min = min(3, steps_req), min(2, steps_req)
+    w_floor = max(0, min(warmup_req, 3) - warmup_done)
+    w_rest = max(0, warmup_req - warmup_done)
+    if remaining_s == float("inf"):
+        return w_rest, steps_req, steps_req
+    fit = int(remaining_s / max(step_s, 1e-6))
+    w = min(w_floor, max(0, fit - k_min - e_min))
+    k, e = k_min, e_min
+    left = fit - w - k - e
+    if left > 0:
+        add = min(left, steps_req - k)
+        k, left = k + add, left - add
+    if left > 0:
+        add = min(left, steps_req - e)
+        e, left = e + add, left - add
+    if left > 0:
+        w += min(left, w_rest - w)
+    return w, k, e
 
 
 class ClockSampler:
@@ -152,21 +189,65 @@ def main() -> int:
     trainer = Trainer(cfg, tc)
     dev = trainer.device
 
-    tokens, targets, seg = trainer.make_global_batch()
-    tokens, targets = tokens.pin_memory(), targets.pin_memory()
+    # a small pool of synthetic batches, cycled, so that no step repeats the batch of the step before it
+    pool = []
+    for _ in range(4):
+        tk, tg, sg = trainer.make_global_batch()
+        pool.append((tk.pin_memory(), tg.pin_memory(), sg))
+    seg = pool[0][2]
+    if seg is not None:  # packed documents: one document layout for all batches (plans and masks are built once)
+        pool = [(tk, torch.where(pool[0][1] < 0, pool[0][1], tg), seg) for tk, tg, _ in pool]
+    n_step = [0]
+
+    def next_batch():
+        n_step[0] += 1
+        return pool[n_step[0] % len(pool)]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up through the public step (also builds plans, symmetric buffers, allocator pools)
-    loss = float("nan")
-    for _ in range(max(args.warmup, 0)):
-        loss = trainer.train_step(tokens, targets, seg)
+    def agree(x: float) -> float:
+        """The same number on every rank (max), so that all ranks run the same number of steps."""
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
 
-    # ---- device-timed steps (inputs resident on the device)
-    tok_d, tgt_d = trainer._tok_dev, trainer._tgt_dev
+    budget = args.time_budget if args.time_budget > 0 else float("inf")
+
+    def remaining() -> float:
+        # 20 s are kept back for the teardown (process-group shutdown, interpreter exit)
+        return budget - (time.perf_counter() - T_START) - 20.0
+
+    # ---- warm-up through the public step (also builds plans, symmetric buffers, allocator pools)
+    loss = float("nan")
+    warm_done = 0
+    step_s = 0.0
+    if args.warmup > 0:
+        barrier()
+        t0 = time.perf_counter()
+        loss = trainer.train_step(*next_batch())
+        barrier()
+        step_s = agree(time.perf_counter() - t0)
+        warm_done = 1
+    more_w, k_steps, e2e_steps = plan_counts(args.warmup, args.steps, warm_done, step_s, agree(remaining()))
+    for _ in range(more_w):
+        t0 = time.perf_counter()
+        loss = trainer.train_step(*next_batch())
+        step_s = time.perf_counter() - t0
+        warm_done += 1
+    if more_w > 0:  # the later warm-up steps give the better estimate (the first one also allocates and plans)
+        barrier()
+        _, k_steps, e2e_steps = plan_counts(warm_done, args.steps, warm_done, agree(step_s), agree(remaining()))
+
+    # ---- device-timed steps (inputs resident on the device; a different batch each step)
+    dev_pool = []
+    for tk, tg, _ in pool:
+        a, b = trainer.shard_batch(tk, tg)
+        dev_pool.append((a.to(dev).contiguous(), b.to(dev).contiguous()))
     ctx = trainer.context(seg)
     sampler = ClockSampler(local)
     barrier()
@@ -174,34 +255,26 @@ def main() -> int:
     launches0 = _lib.launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for i in range(k_steps):
+        tok_d, tgt_d = dev_pool[i % len(dev_pool)]
         loss_t = trainer.device_step(tok_d, tgt_d, ctx)
     e1.record()
     barrier()
-    dev_ms = e0.elapsed_time(e1) / max(1, args.steps)
-    launches = _lib.launches() - launches0
+    dev_ms = agree(e0.elapsed_time(e1) / max(1, k_steps))
+    launches = (_lib.launches() - launches0)
     _lib.check_status(dev)
 
-    t = torch.tensor([dev_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms = float(t[0])
-
-    # ---- end-to-end steps through Trainer.train_step (pinned H2D of inputs, D2H of the loss): the same K
-    # steps, but at most about three minutes of them (a 512K-token step takes most of a minute)
-    e2e_steps = max(1, min(args.steps, int(180.0 / max(dev_ms / 1e3, 1e-3))))
+    # ---- end-to-end steps through Trainer.train_step (pinned H2D of inputs, D2H of the loss)
+    if budget != float("inf"):
+        e2e_steps = max(min(2, args.steps), min(e2e_steps, int(agree(remaining()) / max(dev_ms / 1e3, 1e-3))))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        loss = trainer.train_step(tokens, targets, seg)
+        loss = trainer.train_step(*next_batch())
     barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_ms = agree((time.perf_counter() - t0) * 1e3 / e2e_steps)
     clocks = sampler.stop()
 
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t[0])
     tokens_per_step = global_batch * seq_len
     value = tokens_per_step / (dev_ms / 1e3)
     e2e_value = tokens_per_step / (e2e_ms / 1e3)
@@ -216,8 +289,9 @@ def main() -> int:
     if rank == 0:
         out = {
             "metric": "tokens/sec, LLaMA-7B ring-attention training, 64K tokens/GPU (512K ctx at 8 GPUs)",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True,
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": k_steps,
+            "warmup": warm_done, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "time_budget_s": args.time_budget, "ms_per_step": dev_ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform random tokens, random-init weights (std 0.02)",
             "tokens_per_sec_per_gpu": value / world, "mfu_of_measured_sustained_bf16": mfu,
@@ -231,7 +305,8 @@ def main() -> int:
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": trainer.h2d_bytes_per_step(),
                     "d2h_bytes_per_step": trainer.d2h_bytes_per_step()},
-            "gpu_launches": launches,
+            "gpu_launches": launches, "gpu_launches_per_step": launches / max(1, k_steps),
+            "wall_s": time.perf_counter() - T_START,
             "impl": "ours",
         }
         print(json.dumps(out))

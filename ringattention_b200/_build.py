@@ -1,6 +1,7 @@
 """In-tree build of the sm_100a kernel library.
 
-Every ``csrc/*.cu`` (plus ``csrc/common/*.cu``) is compiled by ``nvcc`` for ``sm_100a`` only and
+The CUDA sources ship inside the package (``ringattention_b200/csrc``), so an installed wheel can build its
+own kernels. Every ``csrc/*.cu`` (plus ``csrc/common/*.cu``) is compiled by ``nvcc`` for ``sm_100a`` only and
 linked into ``ringattention_b200/_C/libringattn_b200.so``. The launchers have a C ABI and are bound
 from Python with :mod:`ctypes` (see :mod:`ringattention_b200.ops._lib`), so no PyTorch headers are
 needed and a full rebuild takes seconds. ``nvcc`` cross-compiles without a GPU.
@@ -19,9 +20,9 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
-ROOT = Path(__file__).resolve().parent.parent
-CSRC = ROOT / "csrc"
-OUT_DIR = Path(__file__).resolve().parent / "_C"
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OUT_DIR = PKG / "_C"
 OBJ_DIR = OUT_DIR / "obj"
 LIB_PATH = OUT_DIR / "libringattn_b200.so"
 
@@ -33,12 +34,23 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     f"-I{CSRC}",
 ]
+# RINGATTN_B200_BOUNDS_CHECK=1 builds the checked variant of the library (libringattn_b200_chk.so): the kernels
+# range-check their global-memory indices and record a violation in the status word instead of making the access
+BOUNDS_CHECK = os.environ.get("RINGATTN_B200_BOUNDS_CHECK") == "1"
+if BOUNDS_CHECK:
+    NVCC_FLAGS.append("-DRA_BOUNDS_CHECK=1")
+    OBJ_DIR = OUT_DIR / "obj_chk"
+    LIB_PATH = OUT_DIR / "libringattn_b200_chk.so"
+
+
+class NvccMissing(RuntimeError):
+    """No CUDA compiler on this machine (the prebuilt library, if any, has to do)."""
 
 
 def _nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
-        raise RuntimeError("nvcc not found; the sm_100a kernels cannot be built")
+        raise NvccMissing("nvcc not found; the sm_100a kernels cannot be built")
     return exe
 
 
@@ -76,6 +88,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     srcs = sources()
     if not srcs:
         raise RuntimeError(f"no CUDA sources under {CSRC}")
+    # one builder at a time: the ranks of a job all come through here at start-up
+    import fcntl
+
+    with open(OBJ_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        return _build_locked(srcs, force, verbose)
+
+
+def _build_locked(srcs, force: bool, verbose: bool) -> Path:
     hdr = _headers_digest()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         results = list(ex.map(lambda s: _compile_one(s, hdr, force, verbose), srcs))

@@ -8,7 +8,7 @@ launch. Embedding table and norm gains are replicated.
 With ``f > 1`` the bf16 working copy of a rank's shard lives in symmetric memory; the other ranks never
 hold a gathered copy of the model. ``lin_fwd`` / ``lin_dgrad`` run the GEMM whose leading CTAs pull the
 remote shards into a scratch while the rest of the grid already computes on the local rows
-(``csrc/gemm_gather_sm100.cu``) - the parameter all-gather is fused into the GEMM that consumes the
+(``ringattention_b200/csrc/gemm_gather_sm100.cu``) - the parameter all-gather is fused into the GEMM that consumes the
 weights. ``lin_wgrad`` produces the full weight gradient shard by shard; gradients are all-reduced by
 the trainer and every rank applies only its own rows.
 """

@@ -44,20 +44,29 @@ def available() -> bool:
 
 
 def lib() -> ctypes.CDLL:
-    """Load (once) and return the kernel library; build it first if it is missing."""
+    """Load (once) and return the kernel library. Unless ``RINGATTN_B200_NO_AUTOBUILD=1``, the incremental build
+    runs first (it compares source digests and does nothing when the library is current), so that a stale
+    shared object is never used after an edit of the CUDA sources. With ``RINGATTN_B200_BOUNDS_CHECK=1`` the
+    checked variant of the library is built and loaded instead."""
     global _LIB
     if _LIB is not None:
         return _LIB
     with _LOCK:
         if _LIB is not None:
             return _LIB
-        if not LIB_PATH.exists():
-            if os.environ.get("RINGATTN_B200_NO_AUTOBUILD") == "1":
-                raise KernelError(f"{LIB_PATH} is missing; run python -m ringattention_b200._build")
-            from .. import _build
+        from .. import _build
 
-            _build.build()
-        handle = ctypes.CDLL(str(LIB_PATH))
+        path = _build.LIB_PATH
+        if os.environ.get("RINGATTN_B200_NO_AUTOBUILD") == "1":
+            if not path.exists():
+                raise KernelError(f"{path} is missing; run python -m ringattention_b200._build")
+        else:
+            try:
+                _build.build()
+            except _build.NvccMissing as e:  # an installed wheel on a machine without the toolkit
+                if not path.exists():
+                    raise KernelError(f"cannot build {path}: {e}") from e
+        handle = ctypes.CDLL(str(path))
         handle.ra_last_error.restype = ctypes.c_char_p
         _LIB = handle
     return _LIB

@@ -83,6 +83,11 @@ class Trainer:
                  device: Optional[torch.device] = None, standalone: bool = False):
         self.cfg = model_cfg
         self.tc = train_cfg
+        tp = mesh.size("tp") if mesh is not None else MeshConfig.parse(train_cfg.mesh).tp
+        if tp != 1:
+            # the tp axis exists so that (dp, fsdp, tp, sp) specs can be written down; the driver model has no
+            # tensor-parallel layers, and tp ranks would be replicas on the same data counted tp times
+            raise ValueError("tensor parallelism is not implemented in this driver: the mesh must have tp = 1")
         self.rank, self.world, self.local_rank = init_distributed()
         if standalone:  # a one-rank replica inside a larger job: joins no collective
             self.rank, self.world = 0, 1

@@ -36,7 +36,7 @@ from ..parallel.symm import SymmRing, peer_bandwidth_probe
 from ..trainer import init_distributed
 from .metrics import measured_peaks
 
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction (GB/s), B200 over NVSwitch
 
 
 def _timed(fn, warmup, iters, world):

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from ..config import LlamaConfig
+from ringattention_b200.config import LlamaConfig
 
 
 def rope_torch(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:

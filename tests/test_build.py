@@ -18,3 +18,29 @@ def test_build_and_symbols():
         assert hasattr(lib, sym), sym
     flags = " ".join(_build.NVCC_FLAGS)
     assert "compute_100a" in flags and "sm_100a" in flags
+
+
+@pytest.mark.skipif(shutil.which("nvcc") is None, reason="nvcc not installed")
+def test_wheel_is_self_contained(tmp_path):
+    """A wheel built from the tree, installed elsewhere, carries the kernel sources and the compiled library and
+    loads it without the source tree."""
+    import os
+    import subprocess
+    import sys
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    dist, site = tmp_path / "dist", tmp_path / "site"
+    r = subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "--no-index",
+                        "-w", str(dist), repo], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    whl = next(dist.glob("ringattention_b200-*.whl"))
+    r = subprocess.run([sys.executable, "-m", "pip", "install", "--no-deps", "--no-index", "--target", str(site),
+                        str(whl)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (site / "ringattention_b200" / "csrc" / "attn_fwd_sm100.cu").exists()
+    code = ("import ctypes, ringattention_b200.ops._lib as L; "
+            f"assert str(L.LIB_PATH).startswith({str(site)!r}), L.LIB_PATH; "
+            "h = ctypes.CDLL(str(L.LIB_PATH)); assert hasattr(h, 'ra_attn_fwd'); print('ok')")
+    env = dict(os.environ, PYTHONPATH=str(site), RINGATTN_B200_NO_AUTOBUILD="1")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr

@@ -29,7 +29,7 @@ def test_rmsnorm_fwd_bwd():
 
 
 def test_rope_roundtrip_and_reference():
-    from ringattention_b200.models.llama_torch import rope_torch
+    from llama_torch import rope_torch
     from ringattention_b200.ops import kernels as K
     from ringattention_b200.ops.flash import Positions
 

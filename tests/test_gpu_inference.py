@@ -57,7 +57,7 @@ def test_small_m_linear():
 def test_prefill_and_greedy_decode_match_full_forward():
     from ringattention_b200.config import LlamaConfig
     from ringattention_b200.models.llama_infer import LlamaInference
-    from ringattention_b200.models.llama_torch import llama_forward_torch
+    from llama_torch import llama_forward_torch
     from ringattention_b200.ops import _lib
 
     cfg = LlamaConfig.named("llama-tiny")

@@ -18,7 +18,7 @@ def _tiny():
 
 def test_gradients_match_torch_model():
     from ringattention_b200.models.llama import LlamaModel
-    from ringattention_b200.models.llama_torch import llama_forward_torch
+    from llama_torch import llama_forward_torch
     from ringattention_b200.ops import _lib
 
     cfg = _tiny()
