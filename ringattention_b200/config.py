@@ -262,6 +262,7 @@ class TrainConfig:
     steps: int = 10
     seed: int = 0
     packed_mean_doc_len: int = 0  # >0: packed documents with geometric lengths (segment ids)
+    zero1: bool = True            # shard fp32 master weights and AdamW moments over the sp/dp replicas
     log_every: int = 1
     ckpt_dir: Optional[str] = None
     ckpt_every: int = 0

@@ -128,10 +128,12 @@ class GatherSchedule:
 
 class FlatParams:
     def __init__(self, cfg: LlamaConfig, device, seed: int = 0, with_optimizer: bool = True,
-                 shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 16):
+                 shard: Tuple[int, int] = (0, 1), fsdp_group=None, gather_ctas: int = 16, zero=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.shard_index, self.shard_count = shard
+        self.zero = zero if (zero is not None and zero[1] > 1) else None
+        zc = self.zero[1] if self.zero else 1
         self.fsdp_group = fsdp_group
         self.gather_ctas = gather_ctas
         f = self.shard_count
@@ -149,7 +151,7 @@ class FlatParams:
             sr = N if f == 1 else _round_up((N + f - 1) // f, 256)
             self.mat[name] = (off, N, Kd, sr)
             off += _round_up(sr * Kd, 64)
-        self.numel_shard = _round_up(off, 1024)
+        self.numel_shard = _round_up(off, 1024 * zc)
         off = 0
         self.rep["embed"] = (off, (V, d))
         off += _round_up(V * d, 64)
@@ -160,7 +162,7 @@ class FlatParams:
                 off += _round_up(d, 64)
         self.rep["nf"] = (off, (d,))
         off += _round_up(d, 64)
-        self.numel_rep = _round_up(off, 1024)
+        self.numel_rep = _round_up(off, 1024 * zc)
         self.index = {**{n: None for n in self.mat}, **{n: None for n in self.rep}}
 
         # ---- storage
@@ -195,10 +197,10 @@ class FlatParams:
         self._init_weights(seed)
         self.p32_s = self.m_s = self.v_s = self.p32_r = self.m_r = self.v_r = None
         if with_optimizer:
-            self.p32_s = self.p16_shard.float()
+            self.p32_s = self.own(self.p16_shard).float()
             self.m_s = torch.zeros_like(self.p32_s)
             self.v_s = torch.zeros_like(self.p32_s)
-            self.p32_r = self.p16_rep.float()
+            self.p32_r = self.own(self.p16_rep).float()
             self.m_r = torch.zeros_like(self.p32_r)
             self.v_r = torch.zeros_like(self.p32_r)
         if f > 1:
@@ -230,6 +232,15 @@ class FlatParams:
                 self.p16_rep[off:off + shape[0]] = 1.0
 
     # ------------------------------------------------------------------ views
+    def own(self, region: torch.Tensor) -> torch.Tensor:
+        """The slice of a flat region (shard region or replicated tail, of any dtype) whose optimizer state
+        this rank keeps: all of it unless the state is sharded over the replicas."""
+        if self.zero is None:
+            return region
+        zi, zc, _ = self.zero
+        n = region.numel() // zc
+        return region[zi * n:(zi + 1) * n]
+
     @property
     def numel_grads(self) -> int:
         return self.shard_count * self.numel_shard + self.numel_rep
@@ -380,21 +391,41 @@ class FlatParams:
         common = dict(step=step, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
                       clip=clip, gnorm_sq=gnorm_sq)
         self.invalidate_gathered()
-        K.adamw_(self.p32_s, self.m_s, self.v_s, self.grad_shard(self.shard_index), self.p16_shard,
-                 decay_end=self.numel_shard, **common)
-        K.adamw_(self.p32_r, self.m_r, self.v_r, self.grad_rep(), self.p16_rep,
-                 decay_end=self.rep_decay_end, **common)
+        rep_start = 0 if self.zero is None else self.zero[0] * (self.numel_rep // self.zero[1])
+        rep_decay = max(0, min(self.p32_r.numel(), self.rep_decay_end - rep_start))
+        K.adamw_(self.p32_s, self.m_s, self.v_s, self.own(self.grad_shard(self.shard_index)),
+                 self.own(self.p16_shard), decay_end=self.p32_s.numel(), **common)
+        K.adamw_(self.p32_r, self.m_r, self.v_r, self.own(self.grad_rep()), self.own(self.p16_rep),
+                 decay_end=rep_decay, **common)
+        self.gather_working_copy()
+
+    def gather_working_copy(self) -> None:
+        """With optimizer state sharded over the replicas, every rank has just updated its slice of the bf16
+        weights: all-gather the slices (in place) so that each rank holds its full shard region and tail."""
+        if self.zero is None:
+            return
+        from ..parallel import gradsync
+
+        zi, zc, zg = self.zero
+        with phase("param_allgather"):
+            gradsync.all_gather_(self.p16_shard, zi, zc, zg)
+            gradsync.all_gather_(self.p16_rep, zi, zc, zg)
 
     def state_dict(self) -> dict:
         return {"p32_s": self.p32_s.cpu(), "m_s": self.m_s.cpu(), "v_s": self.v_s.cpu(),
                 "p32_r": self.p32_r.cpu(), "m_r": self.m_r.cpu(), "v_r": self.v_r.cpu(),
-                "shard": (self.shard_index, self.shard_count)}
+                "shard": (self.shard_index, self.shard_count),
+                "zero": (0, 1) if self.zero is None else (self.zero[0], self.zero[1])}
 
     def load_state_dict(self, st: dict) -> None:
         if tuple(st["shard"]) != (self.shard_index, self.shard_count):
             raise ValueError("checkpoint was written with a different fsdp sharding")
+        mine = (0, 1) if self.zero is None else (self.zero[0], self.zero[1])
+        if tuple(st.get("zero", (0, 1))) != mine:
+            raise ValueError("checkpoint was written with a different sharding of the optimizer state")
         self.invalidate_gathered()
         for k in ("p32_s", "m_s", "v_s", "p32_r", "m_r", "v_r"):
             getattr(self, k).copy_(st[k])
-        self.p16_shard.copy_(self.p32_s)
-        self.p16_rep.copy_(self.p32_r)
+        self.own(self.p16_shard).copy_(self.p32_s)
+        self.own(self.p16_rep).copy_(self.p32_r)
+        self.gather_working_copy()

@@ -9,6 +9,14 @@ per rank instead of 2. With ``f == 1`` it degenerates to the plain all-reduce.
 
 The reduce-scatter is issued as one ``reduce`` per shard (root = the owner), which exists on every
 backend (NCCL, gloo), in buckets so that no single collective exceeds ``bucket`` elements.
+
+Optimizer-state sharding over the replicas (``zero`` arguments below). The ranks that hold the same
+parameters (all sp and dp ranks of one fsdp coordinate) used to keep the full fp32 master weights and both
+AdamW moments each. With ``zero = (index, count, group)`` every such rank owns one of ``count`` equal slices
+of the shard region and of the replicated tail instead: the gradient all-reduce over the replicas becomes a
+reduce-scatter (half the traffic), AdamW runs on the owned slice, and the updated bf16 weights are
+all-gathered in place. On an sp = 8 mesh this takes the optimizer state of the 7B model from 81 GB to 10 GB
+per GPU, which is what lets the context per GPU grow with the ring.
 """
 from __future__ import annotations
 
@@ -45,6 +53,69 @@ def reduce_gradients(g: torch.Tensor, numel_shard: int, n_shards: int, my_shard:
         _bucketed(lambda x: dist.all_reduce(x, group=replica_group), mine, bucket)
     if tail.numel():
         _bucketed(lambda x: dist.all_reduce(x), tail, bucket)
+
+
+def _slice(t: torch.Tensor, index: int, count: int) -> torch.Tensor:
+    n = t.numel() // count
+    return t[index * n:(index + 1) * n]
+
+
+def reduce_scatter_(region: torch.Tensor, index: int, count: int, group) -> torch.Tensor:
+    """Sum ``region`` over ``group`` so that this rank's slice (``index`` of ``count`` equal slices) holds the
+    total; in place, the other slices are left with partial sums. Returns the slice."""
+    assert region.numel() % count == 0
+    mine = _slice(region, index, count)
+    if count == 1:
+        return mine
+    if dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(mine, region, group=group)  # in place: output is input's own slot
+    else:  # gloo has no reduce-scatter: one reduce per slice, root = its owner
+        for i in range(count):
+            dist.reduce(_slice(region, i, count), dst=dist.get_global_rank(group, i), group=group)
+    return mine
+
+
+def all_gather_(region: torch.Tensor, index: int, count: int, group) -> None:
+    """Every rank's slice of ``region`` is current; make the whole region current on all ranks (in place)."""
+    if count == 1:
+        return
+    mine = _slice(region, index, count)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(region, mine, group=group)
+    else:
+        for i in range(count):
+            dist.broadcast(_slice(region, i, count), src=dist.get_global_rank(group, i), group=group)
+
+
+def reduce_gradients_zero(g: torch.Tensor, numel_shard: int, n_shards: int, my_shard: int, fsdp_group,
+                          zero) -> None:
+    """Like :func:`reduce_gradients`, for optimizer state sharded over the replicas: afterwards only this
+    rank's slice of its shard region and its slice of the replicated tail hold the sums over all ranks.
+    ``zero = (index, count, group)``: position among the ranks that share the fsdp coordinate."""
+    zi, zc, zg = zero
+    tail = g[n_shards * numel_shard:]
+    if n_shards > 1:
+        for s in range(n_shards):
+            root = dist.get_global_rank(fsdp_group, s)
+            dist.reduce(g[s * numel_shard:(s + 1) * numel_shard], dst=root, group=fsdp_group)
+        if tail.numel():
+            dist.all_reduce(tail, group=fsdp_group)
+    reduce_scatter_(g[my_shard * numel_shard:(my_shard + 1) * numel_shard], zi, zc, zg)
+    if tail.numel():
+        reduce_scatter_(tail, zi, zc, zg)
+
+
+def global_sumsq_zero(own_slice_sq: torch.Tensor, tail_slice_sq: torch.Tensor, fsdp_group, zero) -> torch.Tensor:
+    """Squared gradient norm of the model from the squared norms of the owned slices: the shard slices of all
+    ranks are disjoint and cover the matrices once; the tail slices cover the tail once per fsdp coordinate."""
+    total = own_slice_sq.clone()
+    tail = tail_slice_sq.clone()
+    if zero[1] > 1:
+        dist.all_reduce(total, group=zero[2])
+        dist.all_reduce(tail, group=zero[2])
+    if fsdp_group is not None and dist.get_world_size(fsdp_group) > 1:
+        dist.all_reduce(total, group=fsdp_group)
+    return total + tail
 
 
 def global_sumsq(own_sq: torch.Tensor, tail_sq: torch.Tensor, fsdp_group=None) -> torch.Tensor:

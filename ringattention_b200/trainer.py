@@ -74,9 +74,12 @@ class Trainer:
     """Owns the model replica of this rank and runs training steps on the mesh.
 
     Mesh semantics: ``sp`` shards the sequence (ring attention), ``dp`` and ``fsdp`` shard the
-    batch; parameters are replicated over ``sp``/``dp``; over ``fsdp`` every GEMM weight, its fp32
+    batch; the bf16 parameters are replicated over ``sp``/``dp``; over ``fsdp`` every GEMM weight, its fp32
     master copy and its AdamW moments are row-sharded, and the shards of the other ranks are pulled
-    inside the GEMM that needs them (see ``models/params.py``).
+    inside the GEMM that needs them (see ``models/params.py``). With ``TrainConfig.zero1`` (the default) the
+    fp32 master weights and the AdamW moments are also cut into equal slices over the sp/dp ranks that
+    hold the same parameters: gradients are reduce-scattered, each rank updates its slice, and the bf16
+    weights are all-gathered (``parallel/gradsync.py``).
     """
 
     def __init__(self, model_cfg: LlamaConfig, train_cfg: TrainConfig, mesh: Optional[DeviceMesh] = None,
@@ -105,9 +108,18 @@ class Trainer:
             raise ValueError("seq_len must be divisible by sp")
         self.B = train_cfg.global_batch // self.batch_groups
         self.S = train_cfg.seq_len // self.sp
+        # ranks that hold the same parameter shard (same fsdp coordinate): they reduce its gradient together,
+        # and (train_cfg.zero1) each keeps one slice of its optimizer state
+        self._replica_group = None
+        if self.world > 1 and not standalone:
+            self._replica_group = self.mesh.replica_group("fsdp") if self.fsdp > 1 else dist.group.WORLD
+        self.zero = None
+        if train_cfg.zero1 and self._replica_group is not None and dist.get_world_size(self._replica_group) > 1:
+            self.zero = (dist.get_rank(self._replica_group), dist.get_world_size(self._replica_group),
+                         self._replica_group)
         params = FlatParams(model_cfg, self.device, seed=train_cfg.seed, with_optimizer=True,
                             shard=(self.fsdp_rank, self.fsdp),
-                            fsdp_group=self.mesh.axis("fsdp").group if self.fsdp > 1 else None)
+                            fsdp_group=self.mesh.axis("fsdp").group if self.fsdp > 1 else None, zero=self.zero)
         self.model = LlamaModel(model_cfg, self.device, params=params)
         self.symm_ring = None
         if self.sp > 1:
@@ -115,10 +127,6 @@ class Trainer:
 
             self.symm_ring = SymmRing(self.mesh.axis("sp").group, self.device)
             self.mesh.axis("sp").symm_ring = self.symm_ring
-        # ranks that hold the same parameter shard (same fsdp coordinate): they all-reduce its gradient
-        self._replica_group = None
-        if self.fsdp > 1 and not standalone:
-            self._replica_group = self.mesh.replica_group("fsdp")
         self.step_idx = 0
         self._sync_token = torch.zeros(1, device=self.device)
         self.gnorm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
@@ -190,9 +198,12 @@ class Trainer:
         """Sum the gradients over the job: all-reduce, or with fsdp > 1 a reduce-scatter over the fsdp
         axis plus an all-reduce of the owned shard over the ranks sharing the fsdp coordinate."""
         P = self.model.params
-        gradsync.reduce_gradients(P.g32, P.numel_shard, P.shard_count, P.shard_index,
-                                  self.mesh.axis("fsdp").group if self.fsdp > 1 else None,
-                                  self._replica_group, bucket)
+        fsdp_group = self.mesh.axis("fsdp").group if self.fsdp > 1 else None
+        if self.zero is not None:
+            gradsync.reduce_gradients_zero(P.g32, P.numel_shard, P.shard_count, P.shard_index, fsdp_group, self.zero)
+            return
+        gradsync.reduce_gradients(P.g32, P.numel_shard, P.shard_count, P.shard_index, fsdp_group,
+                                  self._replica_group if self.fsdp > 1 else None, bucket)
 
     def optimizer_step(self) -> None:
         P, tc = self.model.params, self.tc
@@ -200,7 +211,13 @@ class Trainer:
         clip = float(tc.grad_clip)
         if clip > 0:
             self.gnorm_sq.zero_()
-            if self.fsdp == 1:
+            if self.zero is not None:  # only the owned slices hold full sums
+                tail = torch.zeros_like(self.gnorm_sq)
+                K.sumsq(P.own(P.grad_shard(P.shard_index)), self.gnorm_sq)
+                K.sumsq(P.own(P.grad_rep()), tail)
+                self.gnorm_sq.copy_(gradsync.global_sumsq_zero(
+                    self.gnorm_sq, tail, self.mesh.axis("fsdp").group if self.fsdp > 1 else None, self.zero))
+            elif self.fsdp == 1:
                 K.sumsq(P.g32, self.gnorm_sq)
             else:  # only the owned shard and the replicated tail hold full sums
                 tail = torch.zeros_like(self.gnorm_sq)
