@@ -13,6 +13,7 @@ The GPU path never silently degrades: if the kernel library cannot be loaded the
 """
 from __future__ import annotations
 
+import warnings
 from typing import Any, Callable, Optional, Sequence
 
 import torch
@@ -21,6 +22,26 @@ import torch.utils.checkpoint
 from .config import POLICY_NOTHING_SAVEABLE, BlockwiseKwargs, _policy_name
 from .ops import reference as R
 from .parallel.mesh import AxisContext, resolve_axis
+
+
+_WARNED: set = set()
+
+
+def _warn_fallback(q: torch.Tensor, why: str) -> None:
+    """Tell the user, once per reason, that CUDA tensors are being served by the PyTorch restatement."""
+    if q.is_cuda and why not in _WARNED:
+        _WARNED.add(why)
+        warnings.warn(f"ringattention_b200: {why}; this call runs on the PyTorch path, far slower than the "
+                      "sm_100a kernels (which take bf16 tensors with head_dim 64 or 128 and at most a key bias)",
+                      RuntimeWarning, stacklevel=3)
+
+
+def _fallback_reason(q: torch.Tensor, attn_bias) -> str:
+    if q.dtype != torch.bfloat16:
+        return f"dtype {q.dtype} is not bfloat16"
+    if q.shape[-1] not in (64, 128):
+        return f"head_dim {q.shape[-1]} is not 64 or 128"
+    return "attn_bias has query rows (only a key bias (B, 1|H, 1, S_total) is fused)"
 
 
 def _fused_ok(q: torch.Tensor, attn_bias) -> bool:
@@ -73,6 +94,7 @@ def ringattention(q, k, v, attn_bias=None, segment_ids=None, cache_idx=None, axi
         qq, kk, vv = (t if (t.stride(3) == 1 and not any(s % 8 for s in t.stride()[:3])
                              and t.data_ptr() % 16 == 0) else t.contiguous() for t in (q, k, v))
         return A.RingFlashAttention.apply(qq, kk, vv, plan, _symm_ring_for(axis, q.device))
+    _warn_fallback(q, _fallback_reason(q, attn_bias))
     return R.RingAttentionRef.apply(q, k, v, attn_bias, segment_ids, cache_idx, axis.comm,
                                     float32_logits, kw)
 
@@ -93,15 +115,19 @@ def ringattention_inference(q, k, v, attn_mask=None, axis_name=None, float32_log
 
     ``q (B, q_len, H, D)`` is replicated, ``k, v (B, kv_len, H, D)`` are this rank's cache shard and
     ``attn_mask`` is boolean (True = attend), broadcastable to ``(B, H, q_len, S_total)`` and global
-    on its last axis. On CUDA bf16 the KV cache stays where it is: every rank runs a split-KV kernel
-    over its shard and the per-rank ``(o, lse)`` partials are merged through peer memory; all ranks
-    return the same result as the reference's rotation.
+    on its last axis. On CUDA bf16 the KV cache stays where it is: every rank computes a partial
+    ``(o, lse)`` over its shard (the split-KV decode kernel for up to 8 query rows without gradients, the
+    flash-attention kernel with the mask as a bitmap for longer queries or when gradients are needed) and
+    the partials are merged through peer memory; all ranks return the same result as the reference's
+    rotation. Differentiable w.r.t. q, k, v (ringattention_inference.py:38-64): ``dk``/``dv`` belong to the
+    local shard, ``dq`` is the full gradient of the replicated queries on every rank.
     """
     axis = resolve_axis(axis_name)
     if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
-        from .ops import decode as Dk
+        from .ops import inference as Inf
 
-        return Dk.ring_decode_attention(q, k, v, attn_mask, axis, _symm_ring_for(axis, q.device))
+        return Inf.ring_inference_attention(q, k, v, attn_mask, axis, _symm_ring_for(axis, q.device))
+    _warn_fallback(q, _fallback_reason(q, None))
     return R.RingAttentionInferenceRef.apply(q, k, v, attn_mask, axis.comm, float32_logits)
 
 
@@ -115,13 +141,22 @@ def blockwise_feedforward(feedforward: Callable, inputs: torch.Tensor, chunk_siz
     activation checkpointing when ``policy`` is ``nothing_saveable`` (the reference wraps with
     ``partitioning.remat``; the default ``pre_remat=True`` assumes the caller already did).
     ``static_argnums`` is accepted for signature compatibility. A
-    :class:`~ringattention_b200.ops.ffn.FusedSwiGLU` module runs its chunks on the sm_100a kernels.
+    :class:`~ringattention_b200.ops.ffn.FusedSwiGLU` module as ``feedforward`` runs its chunks on the sm_100a
+    GEMM kernels (activation in the GEMM epilogue, per-chunk recomputation in the backward unless ``policy``
+    with ``pre_remat=False`` says everything is saveable); any other callable is looped over in PyTorch.
     """
     if inputs.dim() != 3:
         raise ValueError("inputs must be (B, S, D)")
     B, S, D = inputs.shape
     if chunk_size <= 0 or S % chunk_size:
         raise ValueError(f"chunk_size {chunk_size} must divide the sequence length {S}")
+    from .ops.ffn import FusedSwiGLU
+
+    if isinstance(feedforward, FusedSwiGLU) and inputs.is_cuda and inputs.dtype == torch.bfloat16:
+        # kernel-backed chunk loop with the policy's recomputation built in (a chunk holds chunk_size tokens
+        # of every batch row, like one scan step of the reference)
+        return feedforward.blockwise(inputs, chunk_size * B if B > 1 else chunk_size,
+                                     policy if not pre_remat else POLICY_NOTHING_SAVEABLE)
     remat = (not pre_remat) and _policy_name(policy) == POLICY_NOTHING_SAVEABLE
     outs = []
     for s0 in range(0, S, chunk_size):

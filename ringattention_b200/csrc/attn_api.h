@@ -18,6 +18,7 @@ struct RaAttnBwdArgs {
   const int* seg_q; const int* seg_k; const int* seg_q_mm; const int* seg_k_mm;
   const float* bias; long long bias_sb, bias_sh;
   unsigned long long seed; unsigned int drop_threshold;
+  const unsigned int* keep; long long keep_sb, keep_sh, keep_sr;  // boolean mask bitmap by kv row, or null
   const void* copy_src; void* copy_dst; long long copy_bytes; int copy_ctas;
   int* status;
   void* stream;

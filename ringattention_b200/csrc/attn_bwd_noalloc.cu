@@ -48,6 +48,18 @@ int scratch_for_current_device(float** out) {
 
 }  // namespace
 
+// Defined next to the kernels they name: make the driver load each kernel's code on the current device.
+extern "C" int ra_attn_bwd_load_kernels(void);
+extern "C" int ra_cast_load_kernels(void);
+
+extern "C" int ra_attn_bwd_noalloc_prepare(void) {
+  float* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);
+  if (rc != ra::kHostOk) return rc;
+  if ((rc = ra_attn_bwd_load_kernels()) != ra::kHostOk) return rc;
+  return ra_cast_load_kernels();
+}
+
 extern "C" int ra_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out,
                                    const void* dout, const float* lse, void* dq, void* dk, void* dv,
                                    int B, int H, int Sq, int Sk, int D, int causal_block_size, int q_off,

@@ -22,6 +22,8 @@
 #include "attn_common.cuh"
 #include "common/host_util.h"
 
+RA_BOUNDS_TRANSLATION_UNIT()
+
 namespace ra {
 namespace attn {
 
@@ -417,6 +419,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           const int base = half * 64 + c * 32;
           const int n = lo - base;
           uint32_t keepw = n <= 0 ? 0xffffffffu : (n >= 32 ? 0u : ~((1u << n) - 1u));
+          if (mk.keep && RA_IN_BOUNDS((qi0 + base) >> 5, 1, mk.keep_sr, kTagAttnMaskBits))
+            keepw &= mk.keep[b * mk.keep_sb + h * mk.keep_sh + static_cast<long long>(row_valid ? kj : mk.Sk - 1) * mk.keep_sr +
+                             ((qi0 + base) >> 5)];
           if (mk.drop_threshold) {
             uint32_t drop = 0;
 #pragma unroll 1
@@ -529,6 +534,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           for (int e = 0; e < 32; ++e) r[e] = 0u;
         }
         if (!row_valid) continue;
+        if (!(RA_IN_BOUNDS(kj, 1, mk.Sk, kTagAttnBwdDkv) && RA_IN_BOUNDS(c * 32, 32, D, kTagAttnBwdDkv))) continue;
         float f[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(r[e]) * mul;
@@ -648,7 +654,7 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, long l
     const float l = lse[(static_cast<long long>(bb) * H + hh) * Sq + q];
     l2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
   }
-  if (lane == 0) {
+  if (lane == 0 && RA_IN_BOUNDS(gw, 1, total, kTagAttnBwdPrep)) {
     lse2[gw] = l2;
     delta[gw] = acc;
   }
@@ -731,6 +737,10 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   p.mask.seed_lo = static_cast<unsigned int>(a->seed & 0xffffffffull);
   p.mask.seed_hi = static_cast<unsigned int>(a->seed >> 32);
   p.mask.drop_threshold = a->drop_threshold;
+  p.mask.keep = a->keep;
+  p.mask.keep_sb = a->keep_sb;
+  p.mask.keep_sh = a->keep_sh;
+  p.mask.keep_sr = a->keep_sr;
   p.scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
   p.lse2 = a->lse2;
@@ -770,6 +780,23 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
     kern<<<static_cast<unsigned>(grid), BWD_THREADS, BwdSmem<64>::TOTAL, s>>>(tq, tk, tv, tdo, tdq, p);
   }
   return check_launch("attn_bwd_kernel");
+}
+
+// Touch every kernel of this file on the current device so that its code is resident before a caller that
+// can no longer afford implicit device allocations launches it (CUDA loads kernels lazily by default).
+extern "C" int ra_attn_bwd_load_kernels(void) {
+  using namespace ra;
+  using namespace ra::attn;
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, attn_bwd_kernel<128>) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa, attn_bwd_kernel<64>) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa, attn_bwd_prep_kernel<128>) != cudaSuccess ||
+      cudaFuncGetAttributes(&fa, attn_bwd_prep_kernel<64>) != cudaSuccess) {
+    set_error("ra_attn_bwd_load_kernels: cudaFuncGetAttributes failed");
+    cudaGetLastError();
+    return kHostLaunchFail;
+  }
+  return kHostOk;
 }
 
 // Backward preprocessing: delta and scaled lse into (B, H, Sq_pad) buffers. o / d_o are

@@ -1,5 +1,6 @@
 // Shared pieces of the attention kernels: position maps, tile visibility, dropout hash.
 #pragma once
+#include "common/bounds.cuh"
 #include "common/sm100.cuh"
 
 namespace ra {
@@ -28,6 +29,11 @@ struct MaskParams {
   long long bias_stride_b, bias_stride_h;
   unsigned int seed_lo, seed_hi;
   unsigned int drop_threshold;  // 0 = dropout off; logit dropped iff hash < threshold
+  // Optional boolean mask as a bitmap (bit set = attend), rows padded to whole 128-column tiles. The forward
+  // reads it by query row (word w of row q: keys 32w..32w+31 of this KV block), the backward by kv row (word w
+  // of row k: queries 32w..32w+31); strides in 32-bit words, row stride a multiple of 4.
+  const uint32_t* keep;
+  long long keep_sb, keep_sh, keep_sr;
 };
 
 // False when every entry of the (128 q x 128 k) tile is masked by the causal rule or because the
@@ -83,7 +89,7 @@ __device__ __forceinline__ int vis_next(const uint32_t* words, int t, int n) {
 // when both tiles lie inside one and the same segment (per-tile min == max, equal on both sides), which
 // holds for most tiles of packed documents much longer than a tile.
 __device__ __forceinline__ bool tile_plain(const MaskParams& m, int b, int qi0, int k0) {
-  if (m.bias || m.drop_threshold) return false;
+  if (m.bias || m.drop_threshold || m.keep) return false;
   if (k0 + 128 > m.Sk || qi0 + 128 > m.Sq) return false;
   if (m.seg_q) {
     if (!m.seg_q_mm) return false;

@@ -16,6 +16,8 @@
 #include "attn_common.cuh"
 #include "common/host_util.h"
 
+RA_BOUNDS_TRANSLATION_UNIT()
+
 namespace ra {
 namespace attn {
 
@@ -368,6 +370,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           const int n = limit - 32 * c;
           keep[c] = n >= 32 ? 0xffffffffu : (n <= 0 ? 0u : ((1u << n) - 1u));
         }
+        if (mk.keep) {
+          uint4 kb = make_uint4(0u, 0u, 0u, 0u);
+          if (RA_IN_BOUNDS((k0 >> 5), 4, mk.keep_sr, kTagAttnMaskBits))
+            kb = *reinterpret_cast<const uint4*>(
+              mk.keep + b * mk.keep_sb + h * mk.keep_sh + static_cast<long long>(row_valid ? qi : mk.Sq - 1) * mk.keep_sr +
+              (k0 >> 5));
+          keep[0] &= kb.x;
+          keep[1] &= kb.y;
+          keep[2] &= kb.z;
+          keep[3] &= kb.w;
+        }
         if (mk.drop_threshold) {
           const unsigned int kpos0 = static_cast<unsigned int>(mk.kmap(k0));
 #pragma unroll
@@ -488,7 +501,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         lse = mxl + __logf(tot);
       }
     }
-    if (row_valid) p.lse_out[lse_idx] = lse;
+    if (row_valid && RA_IN_BOUNDS(lse_idx, 1, static_cast<long long>(p.B) * p.H * mk.Sq, kTagAttnFwdLse))
+      p.lse_out[lse_idx] = lse;
     const float mul = inv_l * w_this;
     const float* oprev_row =
         p.o_prev ? p.o_prev + ((static_cast<long long>(b) * mk.Sq + qi) * p.H + h) * D : nullptr;
@@ -503,7 +517,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = 0u;
       }
-      if (row_valid) {
+      if (row_valid && RA_IN_BOUNDS(qi, 1, mk.Sq, kTagAttnFwdOut) && RA_IN_BOUNDS(c * 32, 32, D, kTagAttnFwdOut)) {
         float f[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * mul;
@@ -581,6 +595,7 @@ struct RaAttnFwdArgs {
   const int* seg_q; const int* seg_k; const int* seg_q_mm; const int* seg_k_mm;
   const float* bias; long long bias_sb, bias_sh;
   unsigned long long seed; unsigned int drop_threshold;
+  const unsigned int* keep; long long keep_sb, keep_sh, keep_sr;  // boolean mask bitmap by query row, or null
   const void* copy_src; void* copy_dst; long long copy_bytes; int copy_ctas;
   int* status;
   void* stream;
@@ -621,6 +636,14 @@ extern "C" int ra_attn_fwd(const RaAttnFwdArgs* a) {
   p.mask.seed_lo = static_cast<unsigned int>(a->seed & 0xffffffffull);
   p.mask.seed_hi = static_cast<unsigned int>(a->seed >> 32);
   p.mask.drop_threshold = a->drop_threshold;
+  p.mask.keep = a->keep;
+  p.mask.keep_sb = a->keep_sb;
+  p.mask.keep_sh = a->keep_sh;
+  p.mask.keep_sr = a->keep_sr;
+  if (a->keep && ((a->keep_sr % 4) || (a->keep_sb % 4) || (a->keep_sh % 4) || (reinterpret_cast<uintptr_t>(a->keep) & 15))) {
+    set_error("ra_attn_fwd: mask bitmap rows must be 16-byte aligned");
+    return kHostBadArg;
+  }
   p.scale_log2 = a->softmax_scale * kLog2e;
   p.out = a->out;
   p.out_fp32 = a->out_fp32;

@@ -105,3 +105,41 @@ int check_launch(const char* what) {
 }  // namespace ra
 
 extern "C" const char* ra_last_error() { return ra::g_err; }
+
+// ---- checked build: sum of the per-translation-unit violation records (see common/bounds.cuh)
+#ifdef RA_BOUNDS_CHECK
+#include "bounds.cuh"
+namespace ra {
+namespace {
+BoundsReader g_readers[32];
+int g_n_readers = 0;
+}  // namespace
+void register_bounds_reader(BoundsReader fn) {
+  if (g_n_readers < 32) g_readers[g_n_readers++] = fn;
+}
+}  // namespace ra
+#endif
+
+// out4 = {violations, tag of the first one, its index, its limit}, summed over the library for the current
+// device (after a device synchronisation); reset != 0 clears the records. Returns 1 in a checked build, 0 in a
+// normal build (out4 zeroed: nothing is checked), negative on a CUDA error.
+extern "C" int ra_bounds_report(unsigned long long* out4, int reset) {
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+#ifdef RA_BOUNDS_CHECK
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  for (int i = 0; i < ra::g_n_readers; ++i) {
+    unsigned long long r[4] = {0, 0, 0, 0};
+    if (ra::g_readers[i](r, reset) != 0) return -1;
+    if (r[0] && !out4[0]) {
+      out4[1] = r[1];
+      out4[2] = r[2];
+      out4[3] = r[3];
+    }
+    out4[0] += r[0];
+  }
+  return 1;
+#else
+  (void)reset;
+  return 0;
+#endif
+}

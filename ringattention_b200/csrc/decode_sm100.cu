@@ -16,7 +16,10 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "common/bounds.cuh"
 #include "common/host_util.h"
+
+RA_BOUNDS_TRANSLATION_UNIT()
 
 namespace ra {
 namespace decode {
@@ -273,7 +276,8 @@ __global__ void decode_merge_kernel(const MergeParams p) {
       const int i = row % p.QL, h = (row / p.QL) % p.H, b = row / (p.QL * p.H);
       oi = ((static_cast<long long>(b) * p.QL + i) * p.H + h) * p.D + d;
     }
-    if (p.out_fp32)
+    if (!RA_IN_BOUNDS(oi, 1, static_cast<long long>(gridDim.x) * p.D, kTagDecodeMerge)) {
+    } else if (p.out_fp32)
       reinterpret_cast<float*>(p.out)[oi] = o;
     else
       reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16(o);

@@ -6,7 +6,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common/bounds.cuh"
 #include "common/host_util.h"
+
+RA_BOUNDS_TRANSLATION_UNIT()
 
 namespace ra {
 namespace ew {
@@ -85,7 +88,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
       unpack8(wr[i], g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = f[e] * rs * g[e];
-      yr[i] = pack8(f);
+      if (RA_IN_BOUNDS(static_cast<long long>(r) * d + i * 8, 8, static_cast<long long>(rows) * d, kTagRmsnorm))
+        yr[i] = pack8(f);
     }
   }
 }
@@ -142,7 +146,7 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
           const float t = rs * (gf[e] * wf[e] - xh * dot);
           o[e] = rr ? o[e] + t : t;
         }
-        outr[i] = pack8(o);
+        if (RA_IN_BOUNDS(off + i * 8, 8, static_cast<long long>(rows) * d, kTagRmsnorm)) outr[i] = pack8(o);
       }
     }
   }
@@ -151,7 +155,8 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
     const int i = threadIdx.x + v * blockDim.x;
     if (i < nv) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) atomicAdd(dw + i * 8 + e, dwacc[v][e]);
+      for (int e = 0; e < 8; ++e)
+        if (RA_IN_BOUNDS(i * 8 + e, 1, d, kTagRmsnorm)) atomicAdd(dw + i * 8 + e, dwacc[v][e]);
     }
   }
 }
@@ -176,6 +181,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long sb, long lo
     const int b = static_cast<int>(t / S);
     const int pos = s < half ? off0 + s : off1 + (s - half);
     __nv_bfloat16* p = x + b * sb + static_cast<long long>(s) * ss + h * sh + v * 8;
+    if (!(RA_IN_BOUNDS(b, 1, B, kTagRope) && RA_IN_BOUNDS(s, 1, S, kTagRope) && RA_IN_BOUNDS(v * 8 + hd2, 8, D, kTagRope)))
+      continue;
     float a[8], c[8];
     unpack8(*reinterpret_cast<const uint4*>(p), a);
     unpack8(*reinterpret_cast<const uint4*>(p + hd2), c);
@@ -212,7 +219,7 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
     unpack8(*reinterpret_cast<const uint4*>(g + F), uf);
 #pragma unroll
     for (int e = 0; e < 8; ++e) gf[e] = gf[e] / (1.f + __expf(-gf[e])) * uf[e];
-    *reinterpret_cast<uint4*>(h + r * F + v * 8) = pack8(gf);
+    if (RA_IN_BOUNDS(r * F + v * 8, 8, rows * F, kTagSwiglu)) *reinterpret_cast<uint4*>(h + r * F + v * 8) = pack8(gf);
   }
 }
 // dgu = [dh * up * silu'(gate) | dh * silu(gate)]; may run in place over gu.
@@ -238,8 +245,10 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* gu, const __nv_bfloat16* 
       uf[e] = df[e] * silu;
       gf[e] = dg;
     }
-    *reinterpret_cast<uint4*>(dgu + o) = pack8(gf);
-    *reinterpret_cast<uint4*>(dgu + o + F) = pack8(uf);
+    if (RA_IN_BOUNDS(o + F, 8, rows * 2 * F, kTagSwiglu)) {
+      *reinterpret_cast<uint4*>(dgu + o) = pack8(gf);
+      *reinterpret_cast<uint4*>(dgu + o + F) = pack8(uf);
+    }
   }
 }
 
@@ -253,7 +262,9 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ tok, const __nv_bfl
     const long long r = idx / nv;
     const int v = static_cast<int>(idx - r * nv);
     int t = tok[r];
+    (void)RA_IN_BOUNDS(t, 1, vocab, kTagEmbeddingToken);
     t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
+    if (RA_IN_BOUNDS(r * d + v * 8, 8, n * d, kTagEmbeddingRow))
     reinterpret_cast<uint4*>(out + r * d)[v] =
         reinterpret_cast<const uint4*>(table + static_cast<long long>(t) * d)[v];
   }
@@ -267,6 +278,7 @@ __global__ void embedding_bwd_kernel(const int* __restrict__ tok, const __nv_bfl
     const long long r = idx / nv;
     const int v = static_cast<int>(idx - r * nv);
     int t = tok[r];
+    (void)RA_IN_BOUNDS(t, 1, vocab, kTagEmbeddingToken);
     t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
     float f[8];
     unpack8(reinterpret_cast<const uint4*>(dy + r * d)[v], f);
@@ -287,6 +299,7 @@ __global__ void xent_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long lon
   __nv_bfloat16* row = logits + r * ld;
   const int nv = V >> 3;
   const int tgt = target[r];
+  if (tgt >= 0) (void)RA_IN_BOUNDS(tgt, 1, V, kTagXentTarget);
   const bool valid = tgt >= 0 && tgt < V;
   const float tgt_logit = valid ? __bfloat162float(row[tgt]) : 0.f;  // read before the row is overwritten
   float mx = -INFINITY;
@@ -318,7 +331,7 @@ __global__ void xent_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long lon
       if (i * 8 + e == tgt) pr -= 1.f;
       f[e] = pr * gs;
     }
-    reinterpret_cast<uint4*>(row)[i] = pack8(f);
+    if (RA_IN_BOUNDS(i * 8, 8, V, kTagXentRow)) reinterpret_cast<uint4*>(row)[i] = pack8(f);
   }
 }
 
@@ -382,7 +395,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
     uint2 o;
     o.x = *reinterpret_cast<uint32_t*>(&lo);
     o.y = *reinterpret_cast<uint32_t*>(&hi);
-    reinterpret_cast<uint2*>(p16)[i] = o;
+    if (RA_IN_BOUNDS(i * 4, 4, n, kTagAdamw)) reinterpret_cast<uint2*>(p16)[i] = o;
   }
 }
 
@@ -399,7 +412,8 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat1
     const float4 a = reinterpret_cast<const float4*>(src + r * src_ld)[2 * v];
     const float4 b = reinterpret_cast<const float4*>(src + r * src_ld)[2 * v + 1];
     const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    *reinterpret_cast<uint4*>(dst + r * dst_ld + v * 8) = pack8(f);
+    if (RA_IN_BOUNDS(r, 1, rows, kTagCast) && RA_IN_BOUNDS(v * 8, 8, d, kTagCast))
+      *reinterpret_cast<uint4*>(dst + r * dst_ld + v * 8) = pack8(f);
   }
 }
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst,
@@ -548,4 +562,69 @@ extern "C" int ra_cast_bf16_f32(const void* src, float* dst, long long n, void* 
   cast_bf16_f32_kernel<<<grid_for(n / 8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(src), dst, n);
   return check_launch("cast_bf16_f32");
+}
+extern "C" int ra_cast_load_kernels(void) {
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, ra::ew::cast_f32_bf16_kernel) != cudaSuccess) {
+    ra::set_error("ra_cast_load_kernels: cudaFuncGetAttributes failed");
+    cudaGetLastError();
+    return ra::kHostLaunchFail;
+  }
+  return ra::kHostOk;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Boolean attention masks as bitmaps for the attention kernels.
+//
+// mask is (B, Hm, Sq, Sk) bytes (non-zero = attend) with element strides sb/sh/sq (0 = broadcast) and a
+// contiguous last dim. Two bitmaps are written, both with rows padded to whole 128-column tiles:
+//   by_q [B][Hm][Sq][Wk]   word w of row q  holds columns k = 32w .. 32w+31   (forward: a thread owns a q row)
+//   by_k [B][Hm][Sk][Wq]   word w of row k  holds rows    q = 32w .. 32w+31   (backward: a thread owns a kv row)
+// with Wk = 4*ceil(Sk/128), Wq = 4*ceil(Sq/128). Bits beyond Sq / Sk are 0. One CTA packs a 32 x 32 patch.
+namespace ra {
+namespace ew {
+__global__ void pack_mask_kernel(const uint8_t* __restrict__ mask, long long sb, long long sh, long long sq,
+                                 uint32_t* __restrict__ by_q, uint32_t* __restrict__ by_k, int Hm, int Sq,
+                                 int Sk, int Wk, int Wq) {
+  __shared__ uint32_t cols[32];  // cols[j] bit i = mask[q0+i][k0+j]
+  const int k0 = blockIdx.x * 32, q0 = blockIdx.y * 32;
+  const int bh = blockIdx.z;
+  const int b = bh / Hm, h = bh - b * Hm;
+  const int lane = threadIdx.x, i = threadIdx.y;  // lane: column inside the patch, i: row inside the patch
+  const int q = q0 + i, k = k0 + lane;
+  bool on = false;
+  if (q < Sq && k < Sk) on = mask[b * sb + h * sh + static_cast<long long>(q) * sq + k] != 0;
+  const uint32_t row_bits = __ballot_sync(0xffffffffu, on);
+  if (lane == 0) {
+    cols[i] = 0;  // reused below as the transposed patch
+  }
+  __syncthreads();
+  if (on) atomicOr(&cols[lane], 1u << i);
+  __syncthreads();
+  if (by_q && lane == 0 && q < Sq && RA_IN_BOUNDS(k0 >> 5, 1, Wk, kTagPackMask))
+    by_q[(static_cast<long long>(bh) * Sq + q) * Wk + (k0 >> 5)] = row_bits;
+  if (by_k && i == 0 && k < Sk && RA_IN_BOUNDS(q0 >> 5, 1, Wq, kTagPackMask))
+    by_k[(static_cast<long long>(bh) * Sk + k) * Wq + (q0 >> 5)] = cols[lane];
+}
+}  // namespace ew
+}  // namespace ra
+
+// by_q / by_k must be zero-filled by the caller (words of the padding columns are never written).
+extern "C" int ra_pack_mask(const void* mask, long long sb, long long sh, long long sq, void* by_q, void* by_k,
+                            int B, int Hm, int Sq, int Sk, void* stream) {
+  using namespace ra;
+  if (B <= 0 || Hm <= 0 || Sq <= 0 || Sk <= 0 || static_cast<long long>(B) * Hm > 65535) {
+    set_error("ra_pack_mask: bad shape");
+    return kHostBadArg;
+  }
+  const int Wk = 4 * ((Sk + 127) / 128), Wq = 4 * ((Sq + 127) / 128);
+  dim3 grid((Sk + 31) / 32, (Sq + 31) / 32, B * Hm), block(32, 32);
+  if (grid.y > 65535) {
+    set_error("ra_pack_mask: too many query rows");
+    return kHostBadArg;
+  }
+  ew::pack_mask_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(mask), sb, sh, sq, static_cast<uint32_t*>(by_q), static_cast<uint32_t*>(by_k),
+      Hm, Sq, Sk, Wk, Wq);
+  return check_launch("pack_mask");
 }

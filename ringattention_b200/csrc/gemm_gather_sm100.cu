@@ -8,6 +8,8 @@
 //   dgrad  : dx[M, Kw] = dy[M, Nw] W[Nw, Kw]     W rows (Nw = reduction dim) sharded -> b_mn = 1
 #include "gemm_kernel.cuh"
 
+RA_BOUNDS_TRANSLATION_UNIT()
+
 namespace ra {
 namespace gemm {
 

@@ -1,6 +1,7 @@
 // Kernel template shared by the plain GEMM (gemm_sm100.cu) and the variant whose B operand is
 // row-sharded over several GPUs and gathered inside the kernel (gemm_gather_sm100.cu).
 #pragma once
+#include "common/bounds.cuh"
 #include "common/host_util.h"
 #include "common/sm100.cuh"
 
@@ -28,6 +29,11 @@ struct Params {
   long long ldr;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of B across the group)
   int* status;
+  // SwiGLU epilogue (forward of a gate/up projection, B = W[2F][K] K-major with rows [gate | up]): every
+  // 256-column tile is made of gate columns [tn*128, tn*128+128) and the matching up columns (two 128-row
+  // TMA loads, tensor map 1), and the epilogue writes silu(gate) * up, F columns of bf16, instead of the
+  // 2F pre-activations. gate and up are rounded to bf16 first, so the result equals the two-pass path.
+  int swiglu_F;  // 0 = off
 };
 
 constexpr int MAX_SHARDS = 8;
@@ -154,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_n = p.swiglu_F ? (p.swiglu_F + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
   // with a sharded B the tile order (B along N) or the k-block order (B along K) is rotated so
@@ -221,6 +227,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
               for (int i = 0; i < BN / 64; ++i)
                 tma_load_2d(b_dst + i * SLAB_BYTES, tma_b, &full[stage], n0 + 64 * i, kr);
+            } else if (!GATHER && p.swiglu_F) {
+              tma_load_2d(b_dst, &tma_bs.m[1], &full[stage], k0, tn * (BN / 2));
+              tma_load_2d(b_dst + B_STAGE_BYTES / 2, &tma_bs.m[1], &full[stage], k0, p.swiglu_F + tn * (BN / 2));
             } else {
               tma_load_2d(b_dst, tma_b, &full[stage], k0, GATHER ? row_in_shard : n0);
             }
@@ -306,6 +315,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
+      if (p.swiglu_F) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_x32(t_row + c * 32, rg);
+          tmem_ld_x32(t_row + BN / 2 + c * 32, ru);
+          tmem_ld_wait();
+          const int col0 = tn * (BN / 2) + c * 32;
+          if (row < p.M && col0 < p.swiglu_F) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col0 + j * 8 < p.swiglu_F) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float gv = __bfloat162float(__float2bfloat16(__uint_as_float(rg[8 * j + e])));
+                  const float uv = __bfloat162float(__float2bfloat16(__uint_as_float(ru[8 * j + e])));
+                  f[e] = gv / (1.f + __expf(-gv)) * uv;
+                }
+                uint4 v;
+                v.x = pack_bf16x2(f[0], f[1]);
+                v.y = pack_bf16x2(f[2], f[3]);
+                v.z = pack_bf16x2(f[4], f[5]);
+                v.w = pack_bf16x2(f[6], f[7]);
+                if (RA_IN_BOUNDS(row, 1, p.M, kTagGemmStore) && RA_IN_BOUNDS(col0 + 8 * j, 8, p.swiglu_F, kTagGemmStore))
+                  *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -325,7 +366,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                       reinterpret_cast<const float*>(p.R) + static_cast<long long>(row) * p.ldr + col0 + 4 * j);
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
-                *reinterpret_cast<float4*>(dst + 4 * j) = v;
+                if (RA_IN_BOUNDS(row, 1, p.M, kTagGemmStore) && RA_IN_BOUNDS(col0 + 4 * j, 4, p.N, kTagGemmStore))
+                  *reinterpret_cast<float4*>(dst + 4 * j) = v;
               }
             }
           } else {
@@ -353,7 +395,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 v.y = pack_bf16x2(f[2], f[3]);
                 v.z = pack_bf16x2(f[4], f[5]);
                 v.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+                if (RA_IN_BOUNDS(row, 1, p.M, kTagGemmStore) && RA_IN_BOUNDS(col0 + 8 * j, 8, p.N, kTagGemmStore))
+                  *reinterpret_cast<uint4*>(dst + 8 * j) = v;
               }
             }
           }

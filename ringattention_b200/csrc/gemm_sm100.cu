@@ -10,21 +10,26 @@
 // products of a linear layer all run through this one kernel without any transposes in memory.
 #include "gemm_kernel.cuh"
 
+RA_BOUNDS_TRANSLATION_UNIT()
+
 namespace ra {
 namespace gemm {
 
 template <int A_MN, int B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream,
+           const CUtensorMap* tb_half = nullptr) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) {
     set_error("gemm: cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
     return kHostLaunchFail;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles_n = p.swiglu_F ? (p.swiglu_F + BN / 2 - 1) / (BN / 2) : (p.N + BN - 1) / BN;
+  const int tiles = ((p.M + BM - 1) / BM) * tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   TmaSet set;
   set.m[0] = tb;
+  if (tb_half) set.m[1] = *tb_half;
   GatherParams g = {};
   kern<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, set, p, g);
   return check_launch("gemm_bf16_kernel");
@@ -64,10 +69,39 @@ extern "C" int ra_gemm_bf16(const void* A, const void* B, void* C, const void* R
     str[0] = static_cast<uint64_t>(ldb) * 2;
     if ((rc = make_tmap_bf16_sw128(&tb, B, 2, dims, str, box)) != 0) return rc;
   }
-  gemm::Params p{C, ldc, M, N, K, c_fp32, R, ldr, group_m > 0 ? group_m : 8, status};
+  gemm::Params p{C, ldc, M, N, K, c_fp32, R, ldr, group_m > 0 ? group_m : 8, status, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!a_mn && !b_mn) return gemm::launch<0, 0>(ta, tb, p, s);
   if (!a_mn && b_mn) return gemm::launch<0, 1>(ta, tb, p, s);
   if (a_mn && !b_mn) return gemm::launch<1, 0>(ta, tb, p, s);
   return gemm::launch<1, 1>(ta, tb, p, s);
+}
+
+
+// H[M,F] (ldh) = silu(A Wg^T) * (A Wu^T) for W = [Wg ; Wu] stored as [2F][ldb] (K contiguous): the gate/up
+// projection of a SwiGLU feed-forward with the activation in the GEMM epilogue, so the (M, 2F) pre-activations
+// are never written. A is [M][lda], K contiguous. F must be a multiple of 8.
+extern "C" int ra_gemm_bf16_swiglu(const void* A, const void* W, void* Hout, int M, int F, int K, long long lda,
+                                   long long ldb, long long ldh, int group_m, int* status, void* stream) {
+  using namespace ra;
+  if (M <= 0 || F <= 0 || K <= 0 || (F % 8) || (lda % 8) || (ldb % 8) || (ldh % 8) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(Hout) & 15)) {
+    set_error("ra_gemm_bf16_swiglu: bad shape/alignment");
+    return kHostBadArg;
+  }
+  CUtensorMap ta, tb, tbh;
+  int rc;
+  uint64_t dims[2], str[1];
+  uint32_t box[2];
+  dims[0] = K; dims[1] = M; box[0] = gemm::BK; box[1] = gemm::BM;
+  str[0] = static_cast<uint64_t>(lda) * 2;
+  if ((rc = make_tmap_bf16_sw128(&ta, A, 2, dims, str, box)) != 0) return rc;
+  dims[0] = K; dims[1] = 2ull * F; box[0] = gemm::BK; box[1] = gemm::BN;
+  str[0] = static_cast<uint64_t>(ldb) * 2;
+  if ((rc = make_tmap_bf16_sw128(&tb, W, 2, dims, str, box)) != 0) return rc;
+  box[1] = gemm::BN / 2;
+  if ((rc = make_tmap_bf16_sw128(&tbh, W, 2, dims, str, box)) != 0) return rc;
+  gemm::Params p{Hout, ldh, M, 2 * F, K, 0, nullptr, 0, group_m > 0 ? group_m : 8, status, F};
+  return gemm::launch<0, 0>(ta, tb, p, static_cast<cudaStream_t>(stream), &tbh);
 }

@@ -21,6 +21,7 @@ import torch
 
 from ..config import POLICY_NOTHING_SAVEABLE, POLICY_SAVE_ATTENTION, BlockwiseKwargs, LlamaConfig
 from ..ops import attention as A
+from ..ops import ffn
 from ..ops import kernels as K
 from ..ops.flash import Positions
 from ..ops.reference import shard_segments
@@ -38,6 +39,38 @@ class StepContext:
     positions: Positions        # global positions of the local tokens (RoPE, masks)
     symm_ring: object = None
     total_tokens: int = 0       # number of target tokens in the whole global batch
+
+
+class _LayerFFNLinears:
+    """The feed-forward products of layer ``l`` on the flat (optionally fsdp-sharded) parameters, in the form
+    ``ops.ffn.ffn_forward`` / ``ffn_backward`` call them."""
+
+    def __init__(self, P: FlatParams, l: int):
+        self.P, self.gu, self.d = P, f"l{l}.wgu", f"l{l}.wd"
+
+    def gate_up(self, x):
+        return self.P.lin_fwd(x, self.gu)
+
+    def gate_up_act(self, x):
+        if self.P.shard_count == 1:
+            with phase("linear"):
+                return K.linear_swiglu(x, self.P.w(self.gu))
+        return K.swiglu_fwd(self.P.lin_fwd(x, self.gu))  # rows gathered inside the GEMM: activation apart
+
+    def down(self, a, out, residual):
+        return self.P.lin_fwd(a, self.d, out=out, residual=residual)
+
+    def down_dgrad(self, dy):
+        return self.P.lin_dgrad(dy, self.d)
+
+    def down_wgrad(self, dy, a):
+        self.P.lin_wgrad(dy, a, self.d)
+
+    def gate_up_wgrad(self, dgu, x):
+        self.P.lin_wgrad(dgu, x, self.gu)
+
+    def gate_up_dgrad(self, dgu, out):
+        return self.P.lin_dgrad(dgu, self.gu, out=out)
 
 
 class LlamaModel:
@@ -86,16 +119,7 @@ class LlamaModel:
         return x2, (h1, rstd1, qkv, attn, lse)
 
     def _ffn_fwd(self, l: int, x2: torch.Tensor, h2: torch.Tensor) -> torch.Tensor:
-        cfg, P = self.cfg, self.params
-        M = x2.shape[0]
-        x3 = torch.empty_like(x2)
-        step = min(cfg.ffn_chunk_size, M)
-        for r0 in range(0, M, step):
-            r1 = min(M, r0 + step)
-            gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
-            a = K.swiglu_fwd(gu)
-            P.lin_fwd(a, f"l{l}.wd", out=x3[r0:r1], residual=x2[r0:r1])
-        return x3
+        return ffn.ffn_forward(_LayerFFNLinears(self.params, l), h2, self.cfg.ffn_chunk_size, residual=x2)
 
     def layer_forward(self, l: int, x: torch.Tensor, ctx: StepContext, keep: bool = False):
         x2, saved = self._attn_block_fwd(l, x, ctx)
@@ -118,17 +142,7 @@ class LlamaModel:
             saved = s + (x2, h2, rstd2)
         h1, rstd1, qkv, attn, lse, x2, h2, rstd2 = saved
         # ---- blockwise FFN backward (each chunk recomputes its activations)
-        dh2 = torch.empty_like(x2)
-        step = min(cfg.ffn_chunk_size, M)
-        for r0 in range(0, M, step):
-            r1 = min(M, r0 + step)
-            gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
-            a = K.swiglu_fwd(gu)
-            da = P.lin_dgrad(dx3[r0:r1], f"l{l}.wd")
-            P.lin_wgrad(dx3[r0:r1], a, f"l{l}.wd")
-            K.swiglu_bwd_(gu, da)
-            P.lin_wgrad(gu, h2[r0:r1], f"l{l}.wgu")
-            P.lin_dgrad(gu, f"l{l}.wgu", out=dh2[r0:r1])
+        dh2 = ffn.ffn_backward(_LayerFFNLinears(P, l), h2, dx3, cfg.ffn_chunk_size)
         dx2 = K.rmsnorm_bwd(dh2, x2, P.w(f"l{l}.n2"), rstd2, P.g(f"l{l}.n2"), dres=dx3)
         del dh2
         # ---- attention block backward

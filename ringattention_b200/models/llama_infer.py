@@ -26,10 +26,12 @@ import torch.distributed as dist
 
 from ..config import LlamaConfig
 from ..ops import decode as Dk
+from ..ops import ffn
 from ..ops import flash
 from ..ops import kernels as K
 from ..ops.flash import MaskSpec, Positions
 from ..parallel.mesh import AxisContext, resolve_axis
+from .llama import _LayerFFNLinears
 from .params import FlatParams
 
 
@@ -116,13 +118,7 @@ class LlamaInference:
                 attn = self._merge_prefill(o_p, lse_p, t)
             x = P.lin_fwd(attn.reshape(B * t, d), f"l{l}.wo", residual=x)
             h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
-            step = min(cfg.ffn_chunk_size, B * t)
-            x3 = torch.empty_like(x)
-            for r0 in range(0, B * t, step):
-                r1 = min(B * t, r0 + step)
-                gu = P.lin_fwd(h2[r0:r1], f"l{l}.wgu")
-                P.lin_fwd(K.swiglu_fwd(gu), f"l{l}.wd", out=x3[r0:r1], residual=x[r0:r1])
-            x = x3
+            x = ffn.ffn_forward(_LayerFFNLinears(P, l), h2, cfg.ffn_chunk_size, residual=x)
         self.length = self.prefill_len = pos0 + Tc
         self.n_rows = n0 + t
         # logits of the globally last token live on the last rank; share them

@@ -97,6 +97,30 @@ def check_status(device=None, reset: bool = True) -> None:
         raise KernelError(f"device status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+BOUNDS_TAGS = {1: "gemm store", 2: "gemm residual", 10: "attention forward out", 11: "attention forward lse",
+               12: "attention forward carry", 13: "attention mask bitmap", 14: "segment ids", 15: "key bias",
+               20: "attention backward dK/dV", 21: "attention backward prep", 30: "rmsnorm", 31: "rope",
+               32: "swiglu", 33: "embedding token id", 34: "embedding row", 35: "cross-entropy target",
+               36: "cross-entropy row", 37: "adamw", 38: "cast", 39: "mask packing", 40: "decode cache row",
+               41: "decode merge", 42: "decode mask", 43: "small-M linear", 50: "peer copy"}
+
+
+def bounds_report(reset: bool = True) -> dict:
+    """Violations recorded by the checked build of the library (``RINGATTN_B200_BOUNDS_CHECK=1``): kernels
+    range-check the indices behind their global-memory accesses, skip an access that is out of range and count
+    it. Returns ``{"checked": bool, "violations": n, "first": {...}}``; synchronises the device."""
+    out = (ctypes.c_ulonglong * 4)()
+    rc = lib().ra_bounds_report(out, int(reset))
+    if rc < 0:
+        raise KernelError("ra_bounds_report failed")
+    rep = {"checked": rc == 1, "violations": int(out[0]), "first": None}
+    if out[0]:
+        idx = int(out[2])
+        rep["first"] = {"access": BOUNDS_TAGS.get(int(out[1]), str(int(out[1]))),
+                        "index": idx - (1 << 64) if idx >= (1 << 63) else idx, "limit": int(out[3])}
+    return rep
+
+
 def stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 

@@ -55,6 +55,8 @@ class MaskSpec:
     bias: Optional[torch.Tensor] = None   # (B, 1|H, Sk) fp32 key bias for this KV block
     seed: int = 0
     pdrop: float = 0.0
+    keep_q: Optional[torch.Tensor] = None  # (B, 1|H, Sq, 4*ceil(Sk/128)) int32 bitmap by query row (forward)
+    keep_k: Optional[torch.Tensor] = None  # (B, 1|H, Sk, 4*ceil(Sq/128)) int32 bitmap by kv row (backward)
 
 
 def seg_tile_minmax(seg: torch.Tensor) -> torch.Tensor:
@@ -86,6 +88,7 @@ class _FwdArgs(ctypes.Structure):
         ("seg_q", c_vp), ("seg_k", c_vp), ("seg_q_mm", c_vp), ("seg_k_mm", c_vp),
         ("bias", c_vp), ("bias_sb", c_ll), ("bias_sh", c_ll),
         ("seed", ctypes.c_ulonglong), ("drop_threshold", ctypes.c_uint),
+        ("keep", c_vp), ("keep_sb", c_ll), ("keep_sh", c_ll), ("keep_sr", c_ll),
         ("copy_src", c_vp), ("copy_dst", c_vp), ("copy_bytes", c_ll), ("copy_ctas", ctypes.c_int),
         ("status", c_vp),
         ("stream", c_vp),
@@ -103,7 +106,33 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
-def _fill_mask(a, mask: MaskSpec, H: int):
+def pack_mask(mask: torch.Tensor, want_q: bool = True, want_k: bool = True):
+    """Pack a boolean ``(B, 1|H, 1|Sq, Sk)`` mask (True = attend) into the two bitmaps the kernels read:
+    by query row for the forward, by kv row for the backward (``MaskSpec.keep_q`` / ``keep_k``). A mask
+    without query rows (a key-padding mask) must be expanded by the caller to the query length first."""
+    assert mask.dim() == 4 and mask.is_cuda
+    m = mask.to(torch.uint8)
+    if m.stride(3) != 1:
+        m = m.contiguous()
+    B, Hm, Sq, Sk = m.shape
+    Wk, Wq = 4 * ((Sk + 127) // 128), 4 * ((Sq + 127) // 128)
+    by_q = torch.zeros(B, Hm, Sq, Wk, device=m.device, dtype=torch.int32) if want_q else None
+    by_k = torch.zeros(B, Hm, Sk, Wq, device=m.device, dtype=torch.int32) if want_k else None
+    _lib.call("ra_pack_mask", c_vp(m.data_ptr()), c_ll(m.stride(0)), c_ll(m.stride(1)), c_ll(m.stride(2)),
+              c_vp(_ptr(by_q)), c_vp(_ptr(by_k)), B, Hm, Sq, Sk, _lib.stream_ptr())
+    return by_q, by_k
+
+
+def _fill_mask(a, mask: MaskSpec, H: int, by_k: bool = False):
+    keep = mask.keep_k if by_k else mask.keep_q
+    if (mask.keep_q is not None or mask.keep_k is not None) and keep is None:
+        raise ValueError("the mask bitmap for this pass is missing (pack_mask builds both)")
+    if keep is not None:
+        assert keep.dtype == torch.int32 and keep.dim() == 4 and keep.is_contiguous()
+        a.keep = keep.data_ptr()
+        a.keep_sb = keep.stride(0)
+        a.keep_sh = keep.stride(1) if keep.shape[1] == H else 0
+        a.keep_sr = keep.stride(2)
     a.causal_block_size = int(mask.causal_block_size or 0)
     a.q_off0, a.q_off1, a.q_half = mask.q_pos.off0, mask.q_pos.off1, mask.q_pos.half
     a.k_off0, a.k_off1, a.k_half = mask.k_pos.off0, mask.k_pos.off1, mask.k_pos.half
@@ -177,6 +206,7 @@ class _BwdArgs(ctypes.Structure):
         ("seg_q", c_vp), ("seg_k", c_vp), ("seg_q_mm", c_vp), ("seg_k_mm", c_vp),
         ("bias", c_vp), ("bias_sb", c_ll), ("bias_sh", c_ll),
         ("seed", ctypes.c_ulonglong), ("drop_threshold", ctypes.c_uint),
+        ("keep", c_vp), ("keep_sb", c_ll), ("keep_sh", c_ll), ("keep_sr", c_ll),
         ("copy_src", c_vp), ("copy_dst", c_vp), ("copy_bytes", c_ll), ("copy_ctas", ctypes.c_int),
         ("status", c_vp),
         ("stream", c_vp),
@@ -230,7 +260,7 @@ def flash_bwd(q, k, v, dout, lse2, delta, mask: MaskSpec, dq_acc, dk, dv, dkv_mo
     a.dkv_mode = dkv_mode
     a.B, a.H, a.Sq, a.Sk, a.D = B, H, Sq, Sk, D
     a.softmax_scale = 1.0 / math.sqrt(D)
-    _fill_mask(a, mask, H)
+    _fill_mask(a, mask, H, by_k=True)
     a.copy_src, a.copy_dst, a.copy_bytes, a.copy_ctas = copy_src, copy_dst, copy_bytes, copy_ctas
     a.status = _lib.status_tensor(dev).data_ptr()
     a.stream = torch.cuda.current_stream().cuda_stream

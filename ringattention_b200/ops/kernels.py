@@ -62,6 +62,21 @@ def linear_fwd(x, w, out=None, residual=None):
     return gemm(x, w, out=out, residual=residual)
 
 
+def linear_swiglu(x, wgu, out=None, group_m: int = 8):
+    """``silu(x Wg^T) * (x Wu^T)`` for ``wgu = [Wg ; Wu]`` of shape ``(2F, K)``: the gate/up projection with the
+    activation in the GEMM epilogue. ``x (M, K)`` -> ``(M, F)`` bf16."""
+    assert x.dtype == torch.bfloat16 and wgu.dtype == torch.bfloat16 and x.dim() == 2 and wgu.dim() == 2
+    assert x.stride(1) == 1 and wgu.stride(1) == 1 and wgu.shape[1] == x.shape[1] and wgu.shape[0] % 2 == 0
+    M, Kd = x.shape
+    F = wgu.shape[0] // 2
+    if out is None:
+        out = torch.empty(M, F, device=x.device, dtype=torch.bfloat16)
+    assert out.shape == (M, F) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    _lib.call("ra_gemm_bf16_swiglu", ptr(x), ptr(wgu), ptr(out), M, F, Kd, c_ll(x.stride(0)),
+              c_ll(wgu.stride(0)), c_ll(out.stride(0)), group_m, _status(), stream_ptr())
+    return out
+
+
 def linear_dgrad(dy, w, out=None, residual=None):
     """``dx = dy W (+ residual)``; ``dy (M,N)``, ``w (N,K)`` read MN-major."""
     return gemm(dy, w, b_mn=True, out=out, residual=residual)

@@ -97,7 +97,7 @@ class SymmRing:
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
         self.timeout_ns = int(float(os.environ.get("RINGATTN_B200_BARRIER_TIMEOUT_S",
-                                                   timeout_s if timeout_s is not None else 120.0)) * 1e9)
+                                                   timeout_s if timeout_s is not None else 10.0)) * 1e9)
         self.copy_ctas = copy_ctas
         self.overlap = True  # False: pull each block with a separate copy kernel before its step (for measurements)
         self.calls = 0

@@ -106,3 +106,91 @@ def test_engine_reuse_after_reset_matches_a_fresh_engine():
     g2, _ = eng.generate(p2, 6, chunk=128)          # resets, re-records the decode graph
     fresh, _ = LlamaInference(cfg, max_context=1024, batch=1, seed=9).generate(p2, 6, chunk=128)
     assert torch.equal(g2, fresh) and eng.length == 384 + 6
+
+
+@pytest.mark.parametrize("ql,S,H,D", [(1, 700, 2, 128), (8, 1111, 3, 64), (100, 900, 2, 128), (2048, 1536, 2, 128)])
+def test_inference_op_any_query_length_with_gradients(ql, S, H, D):
+    """ringattention_inference with a random boolean mask (ringattention_inference.py:8-35) and its VJP (:38-64)
+    against dense fp32 attention, for query lengths on both sides of the 8-row decode kernel."""
+    import ringattention_b200 as rab
+    from ringattention_b200.ops import _lib, reference as R
+
+    B = 2
+    torch.manual_seed(ql)
+    q, k, v = [torch.randn(B, n, H, D, device="cuda").bfloat16().requires_grad_(True) for n in (ql, S, S)]
+    do = torch.randn(B, ql, H, D, device="cuda").bfloat16()
+    mask = torch.rand(B, 1, ql, S, device="cuda") < 0.6
+    mask[..., 0] = True  # no fully masked row: the dense oracle would average over nothing
+    out = rab.ringattention_inference(q, k, v, mask, None)
+    out.backward(do)
+    qf, kf, vf = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = R.dense_attention(qf, kf, vf, extra_masked=~mask, dtype=torch.float32)
+    ref.backward(do.float())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert (out.float() - ref).abs().max() < 0.02
+    for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert (got.float() - want).abs().max() <= 0.02 * want.abs().max() + 1e-3
+    # without gradients the short queries take the split-KV decode kernel: same numbers
+    with torch.no_grad():
+        out2 = rab.ringattention_inference(q, k, v, mask, None)
+    assert (out2.float() - ref).abs().max() < 0.02
+
+
+def test_mask_bitmaps_round_trip():
+    from ringattention_b200.ops import flash
+
+    torch.manual_seed(3)
+    B, Hm, Sq, Sk = 2, 3, 77, 301
+    m = torch.rand(B, Hm, Sq, Sk, device="cuda") < 0.5
+    by_q, by_k = flash.pack_mask(m)
+    bits = torch.arange(32, device="cuda")
+    got_q = ((by_q.unsqueeze(-1) >> bits) & 1).bool().flatten(3)[..., :Sk]        # (B, Hm, Sq, Sk)
+    got_k = ((by_k.unsqueeze(-1) >> bits) & 1).bool().flatten(3)[..., :Sq]        # (B, Hm, Sk, Sq)
+    assert torch.equal(got_q, m)
+    assert torch.equal(got_k, m.transpose(2, 3))
+    # padding bits are zero
+    assert int(((by_q.unsqueeze(-1) >> bits) & 1).flatten(3)[..., Sk:].sum()) == 0
+
+
+@pytest.mark.parametrize("ql,cache_idx", [(128, 384), (100, 411), (1, 639)])
+def test_cache_idx_on_the_fused_path(ql, cache_idx):
+    """``cache_idx``: replicated queries that start at global position ``cache_idx`` against the cache
+    (ringattention_jax.py:31-35), causal, on the fused kernels including gradients."""
+    import ringattention_b200 as rab
+    from ringattention_b200.ops import _lib, reference as R
+
+    B, H, D, Sk = 2, 2, 128, 640
+    torch.manual_seed(cache_idx)
+    q = torch.randn(B, ql, H, D, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(B, Sk, H, D, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(B, Sk, H, D, device="cuda").bfloat16().requires_grad_(True)
+    do = torch.randn(B, ql, H, D, device="cuda").bfloat16()
+    kw = dict(causal_block_size=1, query_chunk_size=128, key_chunk_size=128)
+    out = rab.ringattention(q, k, v, None, None, cache_idx, None, True, kw)
+    out.backward(do)
+    qf, kf, vf = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = R.dense_attention(qf, kf, vf, torch.arange(cache_idx, cache_idx + ql, device="cuda"),
+                            torch.arange(Sk, device="cuda"), causal_block_size=1, dtype=torch.float32)
+    ref.backward(do.float())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert (out.float() - ref).abs().max() < 0.02
+    for got, want in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert (got.float() - want).abs().max() <= 0.02 * want.abs().max() + 1e-3
+
+
+def test_fallback_to_pytorch_path_warns_once():
+    import warnings
+
+    import ringattention_b200 as rab
+    from ringattention_b200 import api
+
+    api._WARNED.clear()
+    q = torch.randn(1, 64, 2, 64, device="cuda")  # fp32: not served by the kernels
+    kw = dict(causal_block_size=1, query_chunk_size=64, key_chunk_size=64)
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        rab.ringattention(q, q, q, None, None, None, None, True, kw)
+        rab.ringattention(q, q, q, None, None, None, None, True, kw)
+    assert sum("PyTorch path" in str(x.message) for x in w) == 1

@@ -38,8 +38,14 @@ def test_gradients_match_torch_model():
     (ref / (B * S)).backward()
     assert abs(loss.item() - ref.item()) / ref.item() < 2e-3
     for n in model.params.index:
-        cos = torch.nn.functional.cosine_similarity(model.params.g(n).flatten(), W[n].grad.flatten(), dim=0)
+        got, want = model.params.g(n).flatten(), W[n].grad.flatten()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=0)
         assert cos > 0.999, (n, cos.item())
+        # cosine is blind to a wrong scale: also the largest error against the largest entry, and the norm ratio
+        rel = ((got - want).abs().max() / want.abs().max()).item()
+        assert rel < 0.06, (n, rel)
+        ratio = (got.norm() / want.norm()).item()
+        assert abs(ratio - 1.0) < 0.02, (n, ratio)
 
 
 def test_remat_policies_agree():
@@ -60,6 +66,7 @@ def test_remat_policies_agree():
     for other in grads[1:]:
         cos = torch.nn.functional.cosine_similarity(grads[0], other, dim=0)
         assert cos > 0.9999
+        assert ((grads[0] - other).abs().max() / grads[0].abs().max()).item() < 0.02
 
 
 def test_loss_curve_and_checkpoint_resume(tmp_path):

@@ -52,10 +52,18 @@ def test_no_alloc_backward_matches_regular_path_twice():
 
     lib = _lib.lib()
     lib.ra_attn_bwd_noalloc.restype = ctypes.c_int
+    lib.ra_attn_bwd_noalloc_prepare.restype = ctypes.c_int
+    # per-device set-up while memory is still to be had: resolves the array's address, loads the kernels
+    assert lib.ra_attn_bwd_noalloc_prepare() == 0, lib.ra_last_error()
+    assert lib.ra_attn_bwd_noalloc_prepare() == 0  # idempotent
     torch.manual_seed(0)
     cases = [  # (B, Sq, Sk, H, D, cbs, q_off, k_off): different shapes so stale scratch would show
         (2, 512, 512, 4, 128, 1, 0, 0),
         (1, 300, 640, 2, 64, 1, 340, 0),
+        # exactly at both limits (4,194,304 dQ elements, 65,536 rows): lse and delta sit right behind the dQ
+        # accumulator in the shared array, so a slip in the carve-up would corrupt one of them
+        (1, 8192, 1024, 8, 64, 1, 0, 0),
+        (2, 512, 512, 4, 128, 1, 0, 0),
     ]
     for (B, Sq, Sk, H, D, cbs, q_off, k_off) in cases:
         q = torch.randn(B, Sq, H, D, device="cuda").bfloat16()
@@ -80,5 +88,10 @@ def test_no_alloc_rejects_oversized_problems():
     z = ctypes.c_void_p(0)
     # 1 x 8192 x 32 x 128 = 33.5M dQ elements, far above the 4,194,304 limit: refused before any launch
     rc = lib.ra_attn_bwd_noalloc(z, z, z, z, z, z, z, z, z, 1, 32, 8192, 8192, 128, 1, 0, 0, z, z)
+    assert rc != 0
+    assert b"too large" in lib.ra_last_error()
+    # the row limit alone: 512 x 1 x 128 x 64 is exactly 4,194,304 dQ elements (allowed) but every one of the
+    # 65,536 (batch, head) pairs pads its single query row to 128 rows of lse/delta: 8,388,608 > 65,536
+    rc = lib.ra_attn_bwd_noalloc(z, z, z, z, z, z, z, z, z, 512, 128, 1, 1, 64, 1, 0, 0, z, z)
     assert rc != 0
     assert b"too large" in lib.ra_last_error()
