@@ -209,13 +209,13 @@ def mesh_parity(rank, world, dev, mesh_text, label, packed=0):
             _lib.check_status()
             worst, name = _grad_errors(tr, P_ref)
             dl = abs(float(loss_sum) / (gb * seq) - loss_ref)
-            ok &= worst < 0.05 and dl < 2e-3
+            ok &= worst < 0.02 and dl < 1e-3
             print(f"[{rank}] {label}: reduced gradients worst rel err {worst:.4f} ({name}), loss diff {dl:.5f}", flush=True)
             ref_losses = [ref.train_step(tokens, targets, seg) for _ in range(5)]
             curves["ref"] = ref_losses
         curves[zero1] = [tr.train_step(tokens, targets, seg) for _ in range(5)]
         d = max(abs(a - b) for a, b in zip(curves[zero1], curves["ref"]))
-        ok &= d < 1e-2 and curves[zero1][-1] < curves[zero1][0]
+        ok &= d < 5e-3 and curves[zero1][-1] < curves[zero1][0]
         print(f"[{rank}] {label} zero1={zero1}: losses {[round(x, 4) for x in curves[zero1]]} vs one device "
               f"{[round(x, 4) for x in curves['ref']]} (max diff {d:.4f})", flush=True)
         last = tr
