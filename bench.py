@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override layer count (debug only; "
                     "a run with this flag is not the headline config)")
     ap.add_argument("--packed-mean-doc-len", type=int, default=0)
+    ap.add_argument("--phase-times", action="store_true",
+                    help="also report device milliseconds per phase of a step (measured in the end-to-end steps)")
     ap.add_argument("--time-budget", type=float, default=600.0,
                     help="wall-clock seconds for the whole run, counted from process start (0 = no limit)")
     return ap.parse_args()
@@ -267,6 +269,12 @@ def main() -> int:
     # ---- end-to-end steps through Trainer.train_step (pinned H2D of inputs, D2H of the loss)
     if budget != float("inf"):
         e2e_steps = max(min(2, args.steps), min(e2e_steps, int(agree(remaining()) / max(dev_ms / 1e3, 1e-3))))
+    timer = None
+    if args.phase_times:
+        from ringattention_b200.utils.tracing import PhaseTimer, set_phase_timer
+
+        timer = PhaseTimer()
+        set_phase_timer(timer)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -274,6 +282,10 @@ def main() -> int:
     barrier()
     e2e_ms = agree((time.perf_counter() - t0) * 1e3 / e2e_steps)
     clocks = sampler.stop()
+    phases = None
+    if timer is not None:
+        set_phase_timer(None)
+        phases = {k: round(v["ms"] / e2e_steps, 2) for k, v in timer.summary().items()}
 
     tokens_per_step = global_batch * seq_len
     value = tokens_per_step / (dev_ms / 1e3)
@@ -309,6 +321,8 @@ def main() -> int:
             "wall_s": time.perf_counter() - T_START,
             "impl": "ours",
         }
+        if phases is not None:
+            out["phase_ms_per_step_rank0"] = phases
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

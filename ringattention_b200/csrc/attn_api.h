@@ -22,6 +22,9 @@ struct RaAttnBwdArgs {
   const void* copy_src; void* copy_dst; long long copy_bytes; int copy_ctas;
   int* status;
   void* stream;
+  // optional, this launch only: device buffer of 4*64*4 int64 on the launch's device that the first compute CTA
+  // fills with SM-clock timestamps of its pipeline phases (null = no tracing)
+  long long* trace;
 };
 
 extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a);

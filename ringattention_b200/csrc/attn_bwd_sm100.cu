@@ -93,7 +93,7 @@ __device__ __forceinline__ void red_add_v4_sys(float* addr, float a, float b, fl
 }
 
 // Phase timestamps (SM clock) for pipeline analysis; only the first compute CTA records, only its
-// first 64 iterations, and only when a trace buffer was registered with ra_set_bwd_trace().
+// first 64 iterations, and only when the launch was given a trace buffer (RaAttnBwdArgs::trace).
 __device__ __forceinline__ void trace_event(long long* trace, bool on, int role, int it, int slot) {
   if (on && it < 64) trace[(role * 64 + it) * 4 + slot] = clock64();
 }
@@ -676,16 +676,6 @@ int make_bshd_map_bwd(CUtensorMap* m, const void* base, int B, int S, int H, int
 }  // namespace
 
 
-namespace {
-long long* g_bwd_trace = nullptr;
-}
-// Register (or clear, with nullptr) a device buffer of 3*64*4 int64 that the first compute CTA of
-// every later backward launch fills with SM-clock timestamps of its pipeline phases.
-extern "C" int ra_set_bwd_trace(long long* buf) {
-  g_bwd_trace = buf;
-  return 0;
-}
-
 extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   using namespace ra;
   using namespace ra::attn;
@@ -758,7 +748,7 @@ extern "C" int ra_attn_bwd(const RaAttnBwdArgs* a) {
   p.copy_n16 = a->copy_bytes / 16;
   p.copy_ctas = (a->copy_src && a->copy_bytes > 0) ? a->copy_ctas : 0;
   p.status = a->status;
-  p.trace = g_bwd_trace;
+  p.trace = a->trace;
   const int nkt = (a->Sk + 127) / 128;
   const long long grid = static_cast<long long>(nkt) * a->H * a->B + p.copy_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);

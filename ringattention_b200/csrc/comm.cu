@@ -59,10 +59,56 @@ __global__ void copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ d
   for (; i < n16; i += stride) dst[i] = src[i];
 }
 
+// rows x row16 units of 16 bytes; source and destination rows are src_ld16 / dst_ld16 units apart.
+__global__ void copy_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, unsigned int rows,
+                                 unsigned int row16, long long src_ld16, long long dst_ld16) {
+  const unsigned long long total = static_cast<unsigned long long>(rows) * row16;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    uint4 v[4];
+    unsigned long long o[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const unsigned long long j = i + u * stride;
+      const unsigned long long r = j / row16;
+      const unsigned int c = static_cast<unsigned int>(j - r * row16);
+      v[u] = src[r * src_ld16 + c];
+      o[u] = r * dst_ld16 + c;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst[o[u]] = v[u];
+  }
+  for (; i < total; i += stride) {
+    const unsigned long long r = i / row16;
+    const unsigned int c = static_cast<unsigned int>(i - r * row16);
+    dst[r * dst_ld16 + c] = src[r * src_ld16 + c];
+  }
+}
+
 }  // namespace comm
 }  // namespace ra
 
 using namespace ra;
+
+// Copy `rows` rows of `row_bytes` bytes between strided buffers (leading dimensions in bytes); everything a
+// multiple of 16 bytes. Used to stage the K/V rows of a fused (B, S, 3, H, D) projection into the symmetric slot.
+extern "C" int ra_copy_rows(const void* src, void* dst, long long rows, long long row_bytes, long long src_ld,
+                            long long dst_ld, void* stream) {
+  if (rows <= 0 || row_bytes <= 0 || (row_bytes % 16) || (src_ld % 16) || (dst_ld % 16) || rows >= (1ll << 32) ||
+      row_bytes / 16 >= (1ll << 32) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_error("ra_copy_rows: sizes, strides and addresses must be multiples of 16 bytes");
+    return kHostBadArg;
+  }
+  const long long total = rows * (row_bytes / 16);
+  long long blocks = (total + 4 * 256 - 1) / (4 * 256);
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  comm::copy_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), static_cast<unsigned int>(rows),
+      static_cast<unsigned int>(row_bytes / 16), src_ld / 16, dst_ld / 16);
+  return check_launch("copy_rows_kernel");
+}
 
 extern "C" int ra_symm_alloc(unsigned long long bytes, void** out) {
   void* p = nullptr;

@@ -11,13 +11,16 @@ of the chunk being prefilled are masked causally at their true positions.
 
 * prefill: the chunk's tokens are split over the ranks for the dense layers; each rank keeps its own
   K/V slice; queries are all-gathered (small), every rank runs the flash kernel against *its own*
-  cache rows, and the per-rank ``(o, lse)`` partials are exchanged and merged;
+  cache rows, and the per-rank ``(o, lse)`` partials are exchanged and merged. Both exchanges are peer
+  stores into symmetric buffers followed by a flag barrier; the only library collective of a prefill
+  chunk is the final broadcast of the logits;
 * decode: the tiny dense layers are computed redundantly on every rank (weights are replicated), the
   new token's K/V go to rank ``i % N`` (i = index of the decoded token), attention runs the split-KV
   kernel on the local rows and merges across GPUs through peer stores.
 """
 from __future__ import annotations
 
+import ctypes
 import time
 from typing import List, Optional
 
@@ -25,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ..config import LlamaConfig
+from ..ops import _lib
 from ..ops import decode as Dk
 from ..ops import ffn
 from ..ops import flash
@@ -67,17 +71,35 @@ class LlamaInference:
         # [position, step] on the device: lets one recorded CUDA graph serve every decode step
         self.state = torch.zeros(2, dtype=torch.int64, device=self.device)
         self._graph = None
+        self._xchg = 0                              # prefill exchanges so far (parity picks the peer-memory buffer)
         self._tok_buf = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self._logits_buf = None
 
     # ------------------------------------------------------------------ helpers
+    def _rows_to(self, src: torch.Tensor, dst_ptr: int, rows: int, row_bytes: int, src_ld: int, dst_ld: int) -> None:
+        """Strided row copy whose destination may be a peer's memory (plain stores over NVLink)."""
+        _lib.call("ra_copy_rows", ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst_ptr), ctypes.c_longlong(rows),
+                  ctypes.c_longlong(row_bytes), ctypes.c_longlong(src_ld), ctypes.c_longlong(dst_ld), _lib.stream_ptr())
+
     def _gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
-        """All-gather along the token dim (dim 1) of a ``(B, t, ...)`` tensor over the sp axis."""
+        """All-gather of a ``(B, t, H, D)`` bf16 tensor along the token dim over the sp axis through peer memory:
+        every rank stores its slice into slot ``rank`` of each peer's ``(B, N*t, H, D)`` buffer and a flag
+        barrier orders the stores before the read. Two buffers alternate, so a rank that is already one exchange
+        ahead never writes into a buffer its peer still reads (it cannot be two ahead: the barrier in between
+        needs that peer)."""
         if self.world == 1:
             return x
-        parts = [torch.empty_like(x) for _ in range(self.world)]
-        dist.all_gather(parts, x.contiguous(), group=self.group)
-        return torch.cat(parts, dim=1)
+        N, ring = self.world, self.symm_ring
+        B, t, H, D = x.shape
+        x = x.contiguous()
+        nb = B * N * t * H * D * 2
+        buf = ring.buffer("prefill_q_all", 2 * nb)
+        slot = self._xchg & 1
+        row = t * H * D * 2                                   # one batch row of one rank's slice, in bytes
+        for r in range(N):
+            self._rows_to(x, buf.peer_ptrs[r] + slot * nb + self.rank * row, B, row, row, N * row)
+        ring.barrier()
+        return buf.local[slot * nb:(slot + 1) * nb].view(torch.bfloat16).view(B, N * t, H, D)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -130,19 +152,29 @@ class LlamaInference:
         return logits
 
     def _merge_prefill(self, o_p: torch.Tensor, lse_p: torch.Tensor, t: int) -> torch.Tensor:
-        """Exchange per-rank partials so that every rank holds the N partials of its own ``t`` query
-        rows, then merge them with the log-sum-exp kernel."""
-        N, B, H, D = self.world, o_p.shape[0], self.H, self.D
-        lse_bth = lse_p.permute(0, 2, 1).contiguous()                          # (B, Tc, H)
-        send_o = o_p.view(B, N, t, H, D).permute(1, 0, 2, 3, 4).contiguous()   # (N, B, t, H, D)
-        send_l = lse_bth.view(B, N, t, H).permute(1, 0, 2, 3).contiguous()     # (N, B, t, H)
-        recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
-        dist.all_to_all_single(recv_o, send_o, group=self.group)
-        dist.all_to_all_single(recv_l, send_l, group=self.group)
+        """Every rank holds a partial ``(o, lse)`` of all ``N*t`` query rows against its own cache rows; rank r
+        needs the N partials of rows ``[r*t, (r+1)*t)``. Each rank stores those rows of its partial straight into
+        slot ``rank`` of rank r's inbox (peer stores), a flag barrier follows, and the log-sum-exp kernel merges
+        the N slots. Two inboxes alternate from exchange to exchange, as in :meth:`_gather_tokens`."""
+        N, B, H, D, ring = self.world, o_p.shape[0], self.H, self.D, self.symm_ring
+        lse_bth = lse_p.permute(0, 2, 1).contiguous()                          # (B, N*t, H), rows like o_p
         rows = B * t * H
+        n_o, n_l = N * rows * D * 4, N * rows * 4                                # bytes per inbox
+        box_o = ring.buffer("prefill_inbox_o", 2 * n_o)
+        box_l = ring.buffer("prefill_inbox_lse", 2 * n_l)
+        slot = self._xchg & 1
+        self._xchg += 1
+        ro, rl = t * H * D * 4, t * H * 4                                        # bytes of one batch row per dest
+        for r in range(N):
+            self._rows_to(o_p.view(B, N, t * H * D)[:, r], box_o.peer_ptrs[r] + slot * n_o + self.rank * B * ro,
+                          B, ro, N * ro, ro)
+            self._rows_to(lse_bth.view(B, N, t * H)[:, r], box_l.peer_ptrs[r] + slot * n_l + self.rank * B * rl,
+                          B, rl, N * rl, rl)
+        ring.barrier()
+        recv_o = box_o.local[slot * n_o:(slot + 1) * n_o].view(torch.float32).view(N, rows, D)
+        recv_l = box_l.local[slot * n_l:(slot + 1) * n_l].view(torch.float32).view(N, rows)
         out = torch.empty(B, t, H, D, device=self.device, dtype=torch.bfloat16)
-        Dk.merge_partials(recv_o.view(N, rows, D).permute(1, 0, 2), recv_l.view(N, rows).permute(1, 0),
-                          H, 0, out=out)
+        Dk.merge_partials(recv_o.permute(1, 0, 2), recv_l.permute(1, 0), H, 0, out=out)
         return out
 
     # ------------------------------------------------------------------ decode

@@ -21,6 +21,7 @@ from . import flash
 from . import kernels as K
 from .flash import MaskSpec, Positions
 from .reference import shard_segments
+from ..utils.tracing import phase
 
 
 @dataclass
@@ -106,8 +107,9 @@ def ring_forward(q, k, v, plan: RingPlan, symm_ring=None, out=None):
 def ring_backward(q, k, v, out, lse, dout, plan: RingPlan, symm_ring=None, dq=None, dk=None, dv=None):
     """Returns ``(dq, dk, dv)`` bf16. ``dq/dk/dv`` may be given as (strided) destination views."""
     B, Sq, H, D = q.shape
-    lse2, delta = flash.flash_bwd_prep(out, dout, lse)
-    dq_acc = torch.zeros(B, Sq, H, D, device=q.device, dtype=torch.float32)
+    with phase("attn_bwd_prep"):
+        lse2, delta = flash.flash_bwd_prep(out, dout, lse)
+        dq_acc = torch.zeros(B, Sq, H, D, device=q.device, dtype=torch.float32)
     if dk is None:
         dk = torch.empty_like(k)
     if dv is None:
@@ -123,13 +125,18 @@ def ring_backward(q, k, v, out, lse, dout, plan: RingPlan, symm_ring=None, dq=No
     if dq is None:
         dq = torch.empty_like(q)
     Sd = dq.stride()
+    with phase("attn_bwd_dq_cast"):
+        _cast_dq(dq_acc, dq, B, Sq, H, D, Sd)
+    return dq, dk, dv
+
+
+def _cast_dq(dq_acc, dq, B, Sq, H, D, Sd):
     if dq.is_contiguous():
         K.cast_f32_to_bf16(dq_acc.view(B * Sq, H * D), dq.view(B * Sq, H * D))
     elif Sd[3] == 1 and Sd[2] == D and Sd[0] == Sq * Sd[1]:
         K.cast_f32_to_bf16(dq_acc.view(B * Sq, H * D), dq.as_strided((B * Sq, H * D), (Sd[1], 1), dq.storage_offset()))
     else:
         dq.copy_(dq_acc)
-    return dq, dk, dv
 
 
 class RingFlashAttention(torch.autograd.Function):

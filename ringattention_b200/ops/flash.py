@@ -210,8 +210,13 @@ class _BwdArgs(ctypes.Structure):
         ("copy_src", c_vp), ("copy_dst", c_vp), ("copy_bytes", c_ll), ("copy_ctas", ctypes.c_int),
         ("status", c_vp),
         ("stream", c_vp),
+        ("trace", c_vp),
     ]
 
+
+# Phase-timestamp buffers by device index: a backward launch on that device records into its buffer
+# (utils.tracing.BackwardPhaseTrace installs and removes them); launches on other devices are not traced.
+BWD_TRACE_BUFFERS: dict = {}
 
 DKV_STORE_BF16 = 0
 DKV_STORE_FP32 = 1
@@ -264,4 +269,6 @@ def flash_bwd(q, k, v, dout, lse2, delta, mask: MaskSpec, dq_acc, dk, dv, dkv_mo
     a.copy_src, a.copy_dst, a.copy_bytes, a.copy_ctas = copy_src, copy_dst, copy_bytes, copy_ctas
     a.status = _lib.status_tensor(dev).data_ptr()
     a.stream = torch.cuda.current_stream().cuda_stream
+    tb = BWD_TRACE_BUFFERS.get(dev.index if dev.index is not None else torch.cuda.current_device())
+    a.trace = 0 if tb is None else tb.data_ptr()
     _lib.call("ra_attn_bwd", ctypes.byref(a))

@@ -28,6 +28,7 @@ import torch.distributed as dist
 
 from ..ops import _lib, flash
 from ..ops import kernels as K
+from ..utils.tracing import phase
 
 c_vp = ctypes.c_void_p
 
@@ -163,10 +164,25 @@ class SymmRing:
         slot = self.calls & 1
         self.calls += 1
         view = own.local[slot * nb:(slot + 1) * nb].view(torch.bfloat16).view(B, S, 2, H, D)
-        view[:, :, 0].copy_(k)
-        view[:, :, 1].copy_(v)
+        with phase("ring_stage_kv"):
+            self._copy_rows(k, view[:, :, 0])
+            self._copy_rows(v, view[:, :, 1])
         slabs = self.scratch("kv_slabs", 2 * nb)
         return own, slot, nb, slabs
+
+    @staticmethod
+    def _copy_rows(src: torch.Tensor, dst: torch.Tensor) -> None:
+        """``dst[b, s] = src[b, s]`` for ``(B, S, H, D)`` views whose ``(H, D)`` block is contiguous and whose
+        tokens are evenly spaced (a slice of a fused QKV projection): one row copy at memory speed."""
+        B, S, H, D = src.shape
+        ok = lambda t: (t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == S * t.stride(1)
+                        and (t.stride(1) * 2) % 16 == 0 and t.data_ptr() % 16 == 0)
+        if (H * D * 2) % 16 or not (ok(src) and ok(dst)):
+            dst.copy_(src)
+            return
+        _lib.call("ra_copy_rows", c_vp(src.data_ptr()), c_vp(dst.data_ptr()), ctypes.c_longlong(B * S),
+                  ctypes.c_longlong(H * D * 2), ctypes.c_longlong(src.stride(1) * 2),
+                  ctypes.c_longlong(dst.stride(1) * 2), _lib.stream_ptr())
 
     def _slab_views(self, slabs, i, nb, B, S, H, D):
         t = slabs[i * nb:(i + 1) * nb].view(torch.bfloat16).view(B, S, 2, H, D)
@@ -186,7 +202,8 @@ class SymmRing:
         B, Sq, H, D = q.shape
         S = k.shape[1]
         own, slot, nb, slabs = self._stage_kv(k, v)
-        self.barrier()
+        with phase("ring_start_barrier"):
+            self.barrier()
         steps = plan.active
         n = len(steps)
         if out is None:
@@ -223,9 +240,11 @@ class SymmRing:
         S = k.shape[1]
         nacc = B * S * 2 * H * D * 4
         acc = self.buffer("dkv_acc", nacc)
-        acc.local[:nacc].zero_()
+        with phase("ring_zero_dkv_acc"):
+            acc.local[:nacc].zero_()
         own, slot, nb, slabs = self._stage_kv(k, v)
-        self.barrier()
+        with phase("ring_start_barrier"):
+            self.barrier()
         steps = plan.active
         n = len(steps)
         for i, st in enumerate(steps):
@@ -242,15 +261,17 @@ class SymmRing:
                 cp = self._maybe_serial_copy(cp)
             flash.flash_bwd(q, kk, vv, dout, lse2, delta, st.mask, dq_acc, t5[:, :, 0], t5[:, :, 1],
                             flash.DKV_REDUCE_FP32, **cp)
-        self.barrier()
+        with phase("ring_end_barrier"):
+            self.barrier()
         a5 = acc.local[:nacc].view(torch.float32).view(B * S, 2, H * D)
-        for which, dst in ((0, dk), (1, dv)):
-            sd = dst.stride()
-            if sd[3] == 1 and sd[2] == D and sd[0] == S * sd[1]:
-                d2 = dst.as_strided((B * S, H * D), (sd[1], 1), dst.storage_offset())
-                K.cast_f32_to_bf16(a5[:, which], d2)
-            else:
-                dst.copy_(a5[:, which].view(B, S, H, D))
+        with phase("ring_cast_dkv"):
+            for which, dst in ((0, dk), (1, dv)):
+                sd = dst.stride()
+                if sd[3] == 1 and sd[2] == D and sd[0] == S * sd[1]:
+                    d2 = dst.as_strided((B * S, H * D), (sd[1], 1), dst.storage_offset())
+                    K.cast_f32_to_bf16(a5[:, which], d2)
+                else:
+                    dst.copy_(a5[:, which].view(B, S, H, D))
 
 
 def peer_bandwidth_probe(ring: SymmRing, nbytes: int = 1 << 30, ctas: int = 64, iters: int = 5) -> dict:

@@ -3,6 +3,7 @@
     python -m ringattention_b200.utils.kbench --kernel attn_fwd --seq 32768 --heads 32
     python -m ringattention_b200.utils.kbench --kernel attn_bwd --seq 16384 --heads 16 --iters 1 --warmup 1
     python -m ringattention_b200.utils.kbench --kernel gemm --m 65536 --n 4096 --k 4096
+    python -m ringattention_b200.utils.kbench --kernel memory_bound --m 65536     # every memory-bound kernel, 7B shapes
 
 Timing: ``--warmup`` untimed launches (>= 3 by default), then ``--iters`` launches between two CUDA
 events on the launching stream with a synchronize on both sides. The operands of the attention
@@ -59,9 +60,64 @@ def time_launches(fn, warmup: int, iters: int, flush_l2: bool) -> float:
     return total / iters
 
 
+def memory_bound_table(args, peak_gbs: float, how: str) -> int:
+    """CUDA-event GB/s of every memory-bound kernel of the driver at the 7B shapes (``--m`` token rows, d_model
+    4096, d_ff 11008, vocab 32000): one JSON line per kernel with its algorithmic bytes (each operand read or
+    written once) and the fraction of the copy bandwidth. The operands exceed the 126 MB L2 at the default size."""
+    dev = "cuda"
+    M, d, F, V, H, D = args.m, 4096, 11008, 32000, 32, 128
+    bf = torch.bfloat16
+    x = torch.randn(M, d, device=dev).to(bf)
+    g = torch.ones(d, device=dev).to(bf)
+    y, rstd = K.rmsnorm_fwd(x, g, 1e-6)
+    dw = torch.zeros(d, device=dev)
+    dx = torch.empty_like(x)
+    from ..ops.flash import Positions
+
+    cases = []
+    cases.append(("rmsnorm_fwd", lambda: K.rmsnorm_fwd(x, g, 1e-6, out=y, rstd=rstd), 2 * M * d * 2))
+    cases.append(("rmsnorm_bwd (+residual)", lambda: K.rmsnorm_bwd(y, x, g, rstd, dw, dres=y, out=dx), 4 * M * d * 2))
+    qk = torch.randn(1, M, 2 * H, D, device=dev).to(bf)
+    cases.append(("rope (q and k heads, in place)", lambda: K.rope_(qk, Positions(0), 10000.0), 2 * qk.numel() * 2))
+    Mc = min(M, 8192)  # the feed-forward and the loss run in chunks of 8192 rows
+    gu = torch.randn(Mc, 2 * F, device=dev).to(bf)
+    hh = torch.empty(Mc, F, device=dev, dtype=bf)
+    cases.append(("swiglu_fwd (8192-row chunk)", lambda: K.swiglu_fwd(gu, out=hh), Mc * 3 * F * 2))
+    cases.append(("swiglu_bwd (8192-row chunk)", lambda: K.swiglu_bwd_(gu, hh), Mc * 5 * F * 2))
+    table = torch.randn(V, d, device=dev).to(bf)
+    tok = torch.randint(0, V, (M,), device=dev, dtype=torch.int32)
+    emb = torch.empty(M, d, device=dev, dtype=bf)
+    dtab = torch.zeros(V, d, device=dev)
+    cases.append(("embedding_fwd", lambda: K.embedding_fwd(tok, table, out=emb), 2 * M * d * 2))
+    cases.append(("embedding_bwd (fp32 scatter-add)", lambda: K.embedding_bwd(tok, emb, dtab), M * d * 2 + 2 * M * d * 4))
+    logits = torch.randn(Mc, V, device=dev).to(bf)
+    tgt = torch.randint(0, V, (Mc,), device=dev, dtype=torch.int32)
+    loss = torch.empty(Mc, device=dev)
+    cases.append(("xent_fwd_bwd (8192-row chunk, in place)", lambda: K.xent_fwd_bwd_(logits, tgt, 1e-4, loss=loss),
+                  2 * Mc * V * 2))
+    n = 1 << 28  # 268M parameters per launch (1 GiB of fp32 each for master, moments and gradient)
+    p32, m1, m2, gr = [torch.zeros(n, device=dev) for _ in range(4)]
+    p16 = torch.empty(n, device=dev, dtype=bf)
+    cases.append(("adamw (fp32 master + moments, bf16 copy)",
+                  lambda: K.adamw_(p32, m1, m2, gr, p16, step=1, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                                   weight_decay=0.1, decay_end=n), n * (7 * 4 + 2)))
+    acc = torch.zeros(1, device=dev)
+    cases.append(("sumsq (gradient norm)", lambda: K.sumsq(gr, acc), n * 4))
+    f32 = torch.randn(M, d, device=dev)
+    cases.append(("cast fp32 -> bf16", lambda: K.cast_f32_to_bf16(f32, emb), M * d * 6))
+    for name, fn, nbytes in cases:
+        ms_t = time_launches(fn, args.warmup, args.iters, args.flush_l2)
+        _lib.check_status()
+        print(json.dumps({"kernel": name, "rows": M, "ms": round(ms_t, 4), "algorithmic_gb": round(nbytes / 1e9, 3),
+                          "gbs": round(nbytes / ms_t / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms_t / 1e6 / peak_gbs, 3),
+                          "denominator": how, "iters": args.iters, "warmup": args.warmup}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad", "decode", "small_m_linear", "sdpa_fwd", "sdpa_bwd"])
+    ap.add_argument("--kernel", required=True, choices=["attn_fwd", "attn_bwd", "gemm", "gemm_dgrad", "gemm_wgrad", "gemm_swiglu", "decode",
+                                                 "small_m_linear", "sdpa_fwd", "sdpa_bwd", "memory_bound"])
     ap.add_argument("--seq", type=int, default=32768)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -81,6 +137,8 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     dev = "cuda"
     res = {"kernel": args.kernel, "denominator": how}
+    if args.kernel == "memory_bound":
+        return memory_bound_table(args, peak_gbs, how)
     if args.kernel.startswith("attn"):
         B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
         q = torch.randn(B, S, H, D, device=dev).bfloat16()
@@ -168,6 +226,11 @@ def main(argv=None) -> int:
             b = torch.randn(N, Kd, device=dev).bfloat16()
             c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             fn = lambda: K.gemm(a, b, out=c)
+        elif args.kernel == "gemm_swiglu":  # h[M,N] = silu(x Wg^T) * (x Wu^T), W = [Wg ; Wu] of 2N rows
+            a = torch.randn(M, Kd, device=dev).bfloat16()
+            b = (torch.randn(2 * N, Kd, device=dev) * 0.05).bfloat16()
+            c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            fn = lambda: K.linear_swiglu(a, b, out=c)
         elif args.kernel == "gemm_dgrad":  # dx[M,N] = dy[M,K] W[K,N]
             a = torch.randn(M, Kd, device=dev).bfloat16()
             b = torch.randn(Kd, N, device=dev).bfloat16()
@@ -178,7 +241,7 @@ def main(argv=None) -> int:
             b = torch.randn(Kd, N, device=dev).bfloat16()
             c = torch.zeros(M, N, device=dev, dtype=torch.float32)
             fn = lambda: K.gemm(a, b, a_mn=True, b_mn=True, out=c, residual=c)
-        flops = 2.0 * M * N * Kd
+        flops = 2.0 * M * N * Kd * (2 if args.kernel == "gemm_swiglu" else 1)
         bytes_ = 2.0 * (M * Kd + N * Kd) + c.element_size() * M * N
         res.update(shape=[M, N, Kd])
     ms_t = time_launches(fn, args.warmup, args.iters, args.flush_l2)

@@ -10,7 +10,6 @@ reduction is measured without a profiler.
 from __future__ import annotations
 
 import contextlib
-import ctypes
 import os
 
 import torch
@@ -100,19 +99,21 @@ class BackwardPhaseTrace:
     >>> tr.cycles_per_iteration()
     """
 
-    def __init__(self):
-        from ..ops import _lib
-
-        self._lib = _lib.lib()
-        self.buf = torch.zeros(4, 64, 4, dtype=torch.int64, device="cuda")
+    def __init__(self, device=None):
+        self.index = torch.cuda.current_device() if device is None else torch.device(device).index
+        self.buf = torch.zeros(4, 64, 4, dtype=torch.int64, device=f"cuda:{self.index}")
 
     def __enter__(self):
-        self._lib.ra_set_bwd_trace(ctypes.c_void_p(self.buf.data_ptr()))
+        from ..ops import flash
+
+        flash.BWD_TRACE_BUFFERS[self.index] = self.buf  # handed to the backward launches of this device only
         return self
 
     def __exit__(self, *exc):
-        torch.cuda.synchronize()
-        self._lib.ra_set_bwd_trace(ctypes.c_void_p(0))
+        from ..ops import flash
+
+        torch.cuda.synchronize(self.index)
+        flash.BWD_TRACE_BUFFERS.pop(self.index, None)
         self.table = self.buf.cpu()
         return False
 
