@@ -171,6 +171,7 @@ def main() -> int:
     from ringattention_b200.config import LlamaConfig, MeshConfig, TrainConfig
     from ringattention_b200.ops import _lib
     from ringattention_b200.trainer import Trainer, init_distributed
+    from ringattention_b200.utils.metrics import device_memory_used_gb
 
     rank, world, local = init_distributed()
     if world != args.gpus:
@@ -319,6 +320,8 @@ def main() -> int:
                     "d2h_bytes_per_step": trainer.d2h_bytes_per_step()},
             "gpu_launches": launches, "gpu_launches_per_step": launches / max(1, k_steps),
             "wall_s": time.perf_counter() - T_START,
+            "peak_torch_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "device_mem_used_gb": device_memory_used_gb(),
             "impl": "ours",
         }
         if phases is not None:

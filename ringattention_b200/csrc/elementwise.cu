@@ -62,82 +62,121 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 }
 
 // ---------------------------------------------------------------------------------- RMSNorm
-// y = x * rsqrt(mean(x^2) + eps) * w ; one CTA per row (grid-stride), d % 8 == 0.
-__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows,
-                                   int d, float eps) {
-  __shared__ float red[32];
+// y = x * rsqrt(mean(x^2) + eps) * w. One warp per row: the row sits in registers (MAXV 16-byte vectors per lane,
+// d <= 256 * MAXV), so x is read once, the sum of squares needs only warp shuffles, and the eight warps of a CTA
+// keep eight rows of loads in flight. A warp takes exactly one row (a grid-stride loop left some warps with one
+// row more than others: 15 % of the time at 64K rows), and two CTAs fit on an SM.
+template <int MAXV>
+__global__ void __launch_bounds__(256, 2) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                          int rows, int d, float eps) {
   const int nv = d >> 3;
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * d);
+  const int lane = threadIdx.x & 31;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (r < rows) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + r * d);
+    uint4 xv[MAXV];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int i = lane + v * 32;
+      xv[v] = i < nv ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
     float ss = 0.f;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
       float f[8];
-      unpack8(xr[i], f);
+      unpack8(xv[v], f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
     }
-    ss = block_sum(ss, red);
+    ss = warp_sum(ss);
     const float rs = rsqrtf(ss / d + eps);
-    if (threadIdx.x == 0 && rstd) rstd[r] = rs;
-    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<long long>(r) * d);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-      float f[8], g[8];
-      unpack8(xr[i], f);
-      unpack8(wr[i], g);
+    if (lane == 0 && rstd) rstd[r] = rs;
+    uint4* yr = reinterpret_cast<uint4*>(y + r * d);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = f[e] * rs * g[e];
-      if (RA_IN_BOUNDS(static_cast<long long>(r) * d + i * 8, 8, static_cast<long long>(rows) * d, kTagRmsnorm))
-        yr[i] = pack8(f);
+    for (int v = 0; v < MAXV; ++v) {
+      const int i = lane + v * 32;
+      if (i < nv) {
+        float f[8], g[8];
+        unpack8(xv[v], f);
+        unpack8(wr[i], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = f[e] * rs * g[e];
+        if (RA_IN_BOUNDS(r * d + i * 8, 8, static_cast<long long>(rows) * d, kTagRmsnorm)) yr[i] = pack8(f);
+      }
     }
   }
 }
 
-// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) ; dw += sum_rows dy * xhat (fp32 atomics,
-// each thread owns fixed columns and accumulates over the rows of its CTA first).
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) ; dw += sum_rows dy * xhat.
+// A row is shared by the four warps of a half CTA (128 threads, MAXV vectors per thread, d <= 1024 * MAXV): x and
+// dy are read once into registers, the gain stays in registers across rows, the row's dot product is combined
+// through shared memory with one 128-thread barrier, and each thread accumulates the gain gradient of its own
+// columns over all rows it sees. The per-CTA partial gain gradients go to `dw_part` (gridDim.x * 2 rows of d
+// floats) and a second kernel sums them: no atomics.
 template <int MAXV>
-__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                                   float* __restrict__ dw, int rows, int d) {
-  __shared__ float red[32];
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          const float* __restrict__ rstd,
+                                                          const __nv_bfloat16* __restrict__ dres,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
+                                                          int rows, int d) {
+  __shared__ float red[2][2][4];  // [half CTA][parity][warp]
   const int nv = d >> 3;
+  const int grp = threadIdx.x >> 7;   // which half of the CTA
+  const int gt = threadIdx.x & 127;   // thread inside the half
+  const int gw = gt >> 5, lane = gt & 31;
   float dwacc[MAXV][8];
+  uint4 wv[MAXV];
 #pragma unroll
-  for (int v = 0; v < MAXV; ++v)
+  for (int v = 0; v < MAXV; ++v) {
+    const int i = gt + v * 128;
+    wv[v] = i < nv ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[v][e] = 0.f;
-  const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const long long off = static_cast<long long>(r) * d;
+  }
+  int par = 0;
+  // the row loop has the same trip count for every thread of a half CTA (the barrier below is per half)
+  for (long long r = static_cast<long long>(blockIdx.x) * 2 + grp; r < rows; r += static_cast<long long>(gridDim.x) * 2) {
+    const long long off = r * d;
     const uint4* xr = reinterpret_cast<const uint4*>(x + off);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
+    uint4 xv[MAXV], gv[MAXV];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int i = gt + v * 128;
+      xv[v] = i < nv ? xr[i] : make_uint4(0u, 0u, 0u, 0u);
+      gv[v] = i < nv ? gr[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
     const float rs = rstd[r];
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
-      const int i = threadIdx.x + v * blockDim.x;
-      if (i < nv) {
-        float xf[8], gf[8], wf[8];
-        unpack8(xr[i], xf);
-        unpack8(gr[i], gf);
-        unpack8(wr[i], wf);
+      float xf[8], gf[8], wf[8];
+      unpack8(xv[v], xf);
+      unpack8(gv[v], gf);
+      unpack8(wv[v], wf);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot += gf[e] * wf[e] * xf[e] * rs;
-      }
+      for (int e = 0; e < 8; ++e) dot += gf[e] * wf[e] * xf[e];
     }
-    dot = block_sum(dot, red) / d;
+    dot = warp_sum(dot);
+    if (lane == 0) red[grp][par][gw] = dot;
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+    dot = (red[grp][par][0] + red[grp][par][1] + red[grp][par][2] + red[grp][par][3]) * rs / d;
+    par ^= 1;  // the next row writes the other slot: no second barrier is needed before it
     uint4* outr = reinterpret_cast<uint4*>(dx + off);
     const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + off) : nullptr;
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
-      const int i = threadIdx.x + v * blockDim.x;
+      const int i = gt + v * 128;
       if (i < nv) {
         float xf[8], gf[8], wf[8], o[8];
-        unpack8(xr[i], xf);
-        unpack8(gr[i], gf);
-        unpack8(wr[i], wf);
+        unpack8(xv[v], xf);
+        unpack8(gv[v], gf);
+        unpack8(wv[v], wf);
         if (rr) unpack8(rr[i], o);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -150,56 +189,75 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
       }
     }
   }
+  float* part = dw_part + (static_cast<long long>(blockIdx.x) * 2 + grp) * d;
 #pragma unroll
   for (int v = 0; v < MAXV; ++v) {
-    const int i = threadIdx.x + v * blockDim.x;
+    const int i = gt + v * 128;
     if (i < nv) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (RA_IN_BOUNDS(i * 8 + e, 1, d, kTagRmsnorm)) atomicAdd(dw + i * 8 + e, dwacc[v][e]);
+      reinterpret_cast<float4*>(part + i * 8)[0] = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+      reinterpret_cast<float4*>(part + i * 8)[1] = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
     }
   }
+}
+
+// dw[c] += sum over the `parts` partial rows; one thread per column, coalesced across the columns.
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ dw_part, float* __restrict__ dw, int parts, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float acc = 0.f;
+  for (int p = 0; p < parts; ++p) acc += dw_part[static_cast<long long>(p) * d + c];
+  if (RA_IN_BOUNDS(c, 1, d, kTagRmsnorm)) dw[c] += acc;
 }
 
 // ---------------------------------------------------------------------------------- RoPE
 // In-place rotation of a (B, S, H, D) view: pairs (i, i + D/2), angle pos * theta^(-2i/D).
 // pos = two-run position map of the local token index (see attn PosMap). sign = +1 fwd, -1 bwd.
+// One warp per token: a lane owns 8 frequencies (a 16-byte vector of the first half of a head and its partner in
+// the second half), computes their sines and cosines once and walks the heads, 32 / (D/16) heads per warp step,
+// so the transcendental work is shared by all heads of the token and the kernel runs at memory speed.
+template <int D>
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long sb, long long ss, long long sh,
-                            int B, int S, int H, int D, int off0, int off1, int half, float log2_theta,
+                            int B, int S, int H, int off0, int off1, int half, float log2_theta,
                             float sign, const long long* __restrict__ pos_ptr) {
   if (pos_ptr) off0 += static_cast<int>(*pos_ptr);  // position kept on the device (decode under a CUDA graph)
-  const int hd2 = D >> 1;
-  const int vec_per_row = hd2 >> 3;  // 8-element vectors in the first half
-  const long long total = static_cast<long long>(B) * S * H * vec_per_row;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int v = static_cast<int>(idx % vec_per_row);
-    long long t = idx / vec_per_row;
-    const int h = static_cast<int>(t % H);
-    t /= H;
+  constexpr int hd2 = D >> 1;
+  constexpr int VPH = hd2 >> 3;    // 16-byte vectors per half head
+  constexpr int HL = 32 / VPH;     // heads per warp step
+  const int lane = threadIdx.x & 31;
+  const int v = lane % VPH, hl = lane / VPH;
+  const long long n_tok = static_cast<long long>(B) * S;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float inv_freq[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) inv_freq[e] = exp2f(-log2_theta * (2.0f * (v * 8 + e) / D));
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < n_tok; t += warps) {
     const int s = static_cast<int>(t % S);
     const int b = static_cast<int>(t / S);
     const int pos = s < half ? off0 + s : off1 + (s - half);
-    __nv_bfloat16* p = x + b * sb + static_cast<long long>(s) * ss + h * sh + v * 8;
-    if (!(RA_IN_BOUNDS(b, 1, B, kTagRope) && RA_IN_BOUNDS(s, 1, S, kTagRope) && RA_IN_BOUNDS(v * 8 + hd2, 8, D, kTagRope)))
-      continue;
-    float a[8], c[8];
-    unpack8(*reinterpret_cast<const uint4*>(p), a);
-    unpack8(*reinterpret_cast<const uint4*>(p + hd2), c);
+    float sn[8], cs[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const int i = v * 8 + e;
-      const float inv_freq = exp2f(-log2_theta * (2.0f * i / D));
-      float sn, cs;
-      sincosf(pos * inv_freq, &sn, &cs);
-      sn *= sign;
-      const float a2 = a[e] * cs - c[e] * sn;
-      const float c2 = c[e] * cs + a[e] * sn;
-      a[e] = a2;
-      c[e] = c2;
+      sincosf(pos * inv_freq[e], &sn[e], &cs[e]);
+      sn[e] *= sign;
     }
-    *reinterpret_cast<uint4*>(p) = pack8(a);
-    *reinterpret_cast<uint4*>(p + hd2) = pack8(c);
+    __nv_bfloat16* row = x + b * sb + static_cast<long long>(s) * ss + v * 8;
+    for (int h = hl; h < H; h += HL) {
+      __nv_bfloat16* p = row + h * sh;
+      if (!(RA_IN_BOUNDS(b, 1, B, kTagRope) && RA_IN_BOUNDS(h, 1, H, kTagRope) && RA_IN_BOUNDS(v * 8 + hd2, 8, D, kTagRope)))
+        continue;
+      float a[8], c[8];
+      unpack8(*reinterpret_cast<const uint4*>(p), a);
+      unpack8(*reinterpret_cast<const uint4*>(p + hd2), c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float a2 = a[e] * cs[e] - c[e] * sn[e];
+        const float c2 = c[e] * cs[e] + a[e] * sn[e];
+        a[e] = a2;
+        c[e] = c2;
+      }
+      *reinterpret_cast<uint4*>(p) = pack8(a);
+      *reinterpret_cast<uint4*>(p + hd2) = pack8(c);
+    }
   }
 }
 
@@ -445,57 +503,84 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int ra_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d,
                               float eps, void* stream) {
-  if (d % 8 || rows <= 0) { set_error("rmsnorm_fwd: d must be a multiple of 8"); return kHostBadArg; }
-  const unsigned grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
-  rmsnorm_fwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(x), static_cast<const bf16*>(w), static_cast<bf16*>(y), rstd, rows, d, eps);
+  if (d % 8 || rows <= 0 || d > 8192) { set_error("rmsnorm_fwd: d must be a multiple of 8 and <= 8192"); return kHostBadArg; }
+  const unsigned grid = static_cast<unsigned>((static_cast<long long>(rows) + 7) / 8);  // one warp per row
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bf16 *xp = static_cast<const bf16*>(x), *wp = static_cast<const bf16*>(w);
+  bf16* yp = static_cast<bf16*>(y);
+  const int nv = d / 8;
+  if (nv <= 32) rmsnorm_fwd_kernel<1><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
+  else if (nv <= 64) rmsnorm_fwd_kernel<2><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
+  else if (nv <= 128) rmsnorm_fwd_kernel<4><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
+  else if (nv <= 256) rmsnorm_fwd_kernel<8><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
+  else if (nv <= 512) rmsnorm_fwd_kernel<16><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
+  else rmsnorm_fwd_kernel<32><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, d, eps);
   return check_launch("rmsnorm_fwd");
 }
 
+// Number of partial gain-gradient rows ra_rmsnorm_bwd writes for `rows` input rows: the caller provides a scratch
+// of that many rows of d floats.
+extern "C" int ra_rmsnorm_bwd_parts(int rows) {
+  const int ctas = rows < sm_count() * 16 ? (rows + 1) / 2 : sm_count() * 8;
+  return (ctas < 1 ? 1 : ctas) * 2;
+}
+
 extern "C" int ra_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
-                              const void* dres, void* dx, float* dw, int rows, int d, void* stream) {
-  if (d % 8 || rows <= 0 || d > 256 * 8 * 4) {
-    set_error("rmsnorm_bwd: d must be a multiple of 8 and <= 8192");
+                              const void* dres, void* dx, float* dw, float* dw_part, int rows, int d, void* stream) {
+  if (d % 8 || rows <= 0 || d > 8192 || !dw_part) {
+    set_error("rmsnorm_bwd: d must be a multiple of 8 and <= 8192, and a scratch for the partial sums is needed");
     return kHostBadArg;
   }
-  const unsigned grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
+  const int parts = ra_rmsnorm_bwd_parts(rows);
+  const unsigned grid = parts / 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bf16 *gp = static_cast<const bf16*>(dy), *xp = static_cast<const bf16*>(x), *wp = static_cast<const bf16*>(w);
+  const bf16* rp = static_cast<const bf16*>(dres);
+  bf16* op = static_cast<bf16*>(dx);
   const int nv = d / 8;
-  if (nv <= 256)
-    rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
-                                               static_cast<const bf16*>(w), rstd,
-                                               static_cast<const bf16*>(dres), static_cast<bf16*>(dx), dw,
-                                               rows, d);
-  else if (nv <= 512)
-    rmsnorm_bwd_kernel<2><<<grid, 256, 0, s>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
-                                               static_cast<const bf16*>(w), rstd,
-                                               static_cast<const bf16*>(dres), static_cast<bf16*>(dx), dw,
-                                               rows, d);
+  if (nv <= 128) rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_part, rows, d);
+  else if (nv <= 256) rmsnorm_bwd_kernel<2><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_part, rows, d);
+  else if (nv <= 512) rmsnorm_bwd_kernel<4><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_part, rows, d);
+  else rmsnorm_bwd_kernel<8><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_part, rows, d);
+  int rc = check_launch("rmsnorm_bwd");
+  if (rc != kHostOk) return rc;
+  rmsnorm_dw_reduce_kernel<<<(d + 255) / 256, 256, 0, s>>>(dw_part, dw, parts, d);
+  return check_launch("rmsnorm_dw_reduce");
+}
+
+static int launch_rope(void* x, long long sb, long long ss, long long sh, int B, int S, int H, int D, int off0,
+                       int off1, int half, float theta, float sign, const long long* pos_ptr, void* stream) {
+  const long long work = static_cast<long long>(B) * S * 32;  // one warp per token
+  const unsigned grid = grid_for(work, 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bf16* xp = static_cast<bf16*>(x);
+  const float l2t = log2f(theta);
+  if (D == 64)
+    rope_kernel<64><<<grid, 256, 0, st>>>(xp, sb, ss, sh, B, S, H, off0, off1, half, l2t, sign, pos_ptr);
+  else if (D == 128)
+    rope_kernel<128><<<grid, 256, 0, st>>>(xp, sb, ss, sh, B, S, H, off0, off1, half, l2t, sign, pos_ptr);
   else
-    rmsnorm_bwd_kernel<4><<<grid, 256, 0, s>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
-                                               static_cast<const bf16*>(w), rstd,
-                                               static_cast<const bf16*>(dres), static_cast<bf16*>(dx), dw,
-                                               rows, d);
-  return check_launch("rmsnorm_bwd");
+    rope_kernel<256><<<grid, 256, 0, st>>>(xp, sb, ss, sh, B, S, H, off0, off1, half, l2t, sign, pos_ptr);
+  return check_launch("rope");
 }
 
 extern "C" int ra_rope(void* x, long long sb, long long ss, long long sh, int B, int S, int H, int D,
                        int off0, int off1, int half, float theta, int inverse, void* stream) {
-  if (D % 16 || B <= 0 || S <= 0) { set_error("rope: head_dim must be a multiple of 16"); return kHostBadArg; }
-  const long long work = static_cast<long long>(B) * S * H * (D / 16);
-  rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<bf16*>(x), sb, ss, sh, B, S, H, D, off0, off1, half, log2f(theta), inverse ? -1.f : 1.f, nullptr);
-  return check_launch("rope");
+  if ((D != 64 && D != 128 && D != 256) || B <= 0 || S <= 0) {
+    set_error("rope: head_dim must be 64, 128 or 256");
+    return kHostBadArg;
+  }
+  return launch_rope(x, sb, ss, sh, B, S, H, D, off0, off1, half, theta, inverse ? -1.f : 1.f, nullptr, stream);
 }
 
 // Same rotation with the position of token 0 read from device memory (off0 is added to it).
 extern "C" int ra_rope_at(void* x, long long sb, long long ss, long long sh, int B, int S, int H, int D,
                           int off0, const long long* pos_ptr, float theta, void* stream) {
-  if (D % 16 || B <= 0 || S <= 0 || !pos_ptr) { set_error("rope_at: bad arguments"); return kHostBadArg; }
-  const long long work = static_cast<long long>(B) * S * H * (D / 16);
-  rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<bf16*>(x), sb, ss, sh, B, S, H, D, off0, 0, 1 << 30, log2f(theta), 1.f, pos_ptr);
-  return check_launch("rope_at");
+  if ((D != 64 && D != 128 && D != 256) || B <= 0 || S <= 0 || !pos_ptr) {
+    set_error("rope_at: bad arguments");
+    return kHostBadArg;
+  }
+  return launch_rope(x, sb, ss, sh, B, S, H, D, off0, 0, 1 << 30, theta, 1.f, pos_ptr, stream);
 }
 
 extern "C" int ra_swiglu_fwd(const void* gu, void* h, long long rows, int F, void* stream) {

@@ -107,8 +107,10 @@ def rmsnorm_bwd(dy, x, w, rstd, dw_acc, dres=None, out=None):
     assert dy.is_contiguous() and x.is_contiguous() and dw_acc.dtype == torch.float32
     if out is None:
         out = torch.empty_like(x)
+    parts = _lib.lib().ra_rmsnorm_bwd_parts(rows)
+    scratch = torch.empty(parts, d, device=x.device, dtype=torch.float32)  # per-CTA partial gain gradients
     _lib.call("ra_rmsnorm_bwd", ptr(dy), ptr(x), ptr(w), ptr(rstd), ptr(dres), ptr(out), ptr(dw_acc),
-              rows, d, stream_ptr())
+              ptr(scratch), rows, d, stream_ptr(), n_kernels=2)
     return out
 
 

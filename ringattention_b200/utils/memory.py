@@ -3,8 +3,8 @@
     python -m ringattention_b200.utils.memory --model llama-7b --gpus 1 2 4 8
 
 The model mirrors what the driver allocates (``models/params.py``, ``models/llama.py``,
-``parallel/symm.py``): bf16 weights, fp32 master + two AdamW moments (sharded over fsdp), fp32
-gradients (full size), one saved layer input per layer (``nothing_saveable``), the working set of one
+``parallel/symm.py``): bf16 weights, fp32 master + two AdamW moments (sharded over fsdp, and with
+``zero1`` also over the sp/dp ranks that hold the same parameters), fp32 gradients (full size), one saved layer input per layer (``nothing_saveable``), the working set of one
 layer being recomputed and differentiated, the chunked FFN / LM-head temporaries and, for sp > 1,
 the symmetric KV slots, the two local slabs, the fp32 dK/dV accumulator and the fp32 output carry.
 Activation memory is linear in the tokens per GPU, so the maximum context grows linearly with the
@@ -21,7 +21,8 @@ from ..config import LlamaConfig
 GiB = 1024 ** 3
 
 
-def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int = 1, batch: int = 1) -> dict:
+def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int = 1, batch: int = 1,
+                  zero1: bool = True, dp: int = 1) -> dict:
     n_mat = cfg.n_layers * (4 * cfg.d_model ** 2 + 3 * cfg.d_model * cfg.d_ff) + cfg.vocab_size * cfg.d_model
     n_rep = cfg.vocab_size * cfg.d_model + (2 * cfg.n_layers + 1) * cfg.d_model
     T = tokens_per_gpu * batch
@@ -29,7 +30,8 @@ def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int 
     # sharded weights: own shard + the landing area of gathered shards (two regions per kind of matrix)
     landing = 0 if fsdp == 1 else 2 * (fsdp - 1) / fsdp * 2 * (4 * d * d + 3 * F * d + V * d)
     weights = (n_mat / fsdp + n_rep) * 2 + landing
-    optimizer = (n_mat / fsdp + n_rep) * 12
+    replicas = sp * dp if zero1 else 1   # ranks that share a parameter shard each keep one slice of its state
+    optimizer = (n_mat / fsdp + n_rep) * 12 / replicas
     grads = (n_mat + n_rep) * 4
     saved = cfg.n_layers * T * d * 2
     # one layer in flight (recompute + backward): x2, h1, h2, qkv, attn, dqkv, dattn/dh buffers, dq fp32, lse/delta
@@ -44,13 +46,14 @@ def bytes_per_gpu(cfg: LlamaConfig, tokens_per_gpu: int, sp: int = 1, fsdp: int 
             "layer_working_set": layer, "chunk_temporaries": chunks, "ring_buffers": ring, "total": total}
 
 
-def max_context(cfg: LlamaConfig, gpus: int, hbm_bytes: float = 178 * GiB, fsdp: int = 1, reserve: float = 0.06) -> int:
+def max_context(cfg: LlamaConfig, gpus: int, hbm_bytes: float = 178 * GiB, fsdp: int = 1, reserve: float = 0.06,
+                zero1: bool = True) -> int:
     """Largest global sequence (multiple of 1024 tokens per GPU) that fits with sp = gpus / fsdp."""
     sp = gpus // fsdp
     lo, hi = 0, 1 << 24
     while hi - lo > 1024:
         mid = (lo + hi) // 2 // 1024 * 1024
-        if bytes_per_gpu(cfg, mid, sp, fsdp)["total"] <= hbm_bytes * (1 - reserve):
+        if bytes_per_gpu(cfg, mid, sp, fsdp, zero1=zero1)["total"] <= hbm_bytes * (1 - reserve):
             lo = mid
         else:
             hi = mid
@@ -77,13 +80,14 @@ def main(argv=None) -> int:
     ap.add_argument("--model", default="llama-7b")
     ap.add_argument("--gpus", type=int, nargs="+", default=[1, 2, 4, 8])
     ap.add_argument("--fsdp", type=int, default=1)
+    ap.add_argument("--no-zero1", action="store_true", help="optimizer state replicated over sp (as before zero1)")
     ap.add_argument("--inference-batch", type=int, default=0,
                     help="also print the longest inference context for this batch size")
     args = ap.parse_args(argv)
     cfg = LlamaConfig.named(args.model)
     for g in args.gpus:
-        ctx = max_context(cfg, g, fsdp=args.fsdp)
-        b = bytes_per_gpu(cfg, ctx // max(1, g // args.fsdp), g // args.fsdp, args.fsdp)
+        ctx = max_context(cfg, g, fsdp=args.fsdp, zero1=not args.no_zero1)
+        b = bytes_per_gpu(cfg, ctx // max(1, g // args.fsdp), g // args.fsdp, args.fsdp, zero1=not args.no_zero1)
         print(json.dumps({"gpus": g, "fsdp": args.fsdp, "max_context_tokens": ctx,
                           "gib_per_gpu": {k: round(v / GiB, 1) for k, v in b.items()}}))
         if args.inference_batch:

@@ -57,4 +57,11 @@ def step_metrics(trainer, step_ms: float, loss: float) -> Dict[str, Any]:
     mfu = trainer.model_flops_per_step() / (step_ms / 1e3) / (trainer.world * peaks["bf16_tflops_sustained"] * 1e12)
     return {"step": trainer.step_idx, "loss": loss, "ms_per_step": step_ms, "tokens_per_s": tps,
             "tokens_per_s_per_gpu": tps / trainer.world, "mfu": mfu, "mfu_denominator": peaks["source"],
-            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9, "device_mem_used_gb": device_memory_used_gb()}
+
+
+def device_memory_used_gb() -> float:
+    """Bytes of the current device that are in use by anyone, in GB: PyTorch's pools (which keep their peak) plus the
+    symmetric buffers this package allocates outside of them."""
+    free, total = torch.cuda.mem_get_info()
+    return (total - free) / 1e9

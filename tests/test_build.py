@@ -28,7 +28,12 @@ def test_wheel_is_self_contained(tmp_path):
     import subprocess
     import sys
 
-    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    # build from a copy, so that setuptools leaves its build/ and egg-info directories outside the repository
+    # (the object files travel with the copy: nothing is recompiled)
+    repo = str(tmp_path / "src")
+    shutil.copytree(src, repo, ignore=shutil.ignore_patterns(".git", "_work", "gpurun_out", "baseline", "profiles",
+                                                             "__pycache__", ".pytest_cache", "build", "*.egg-info"))
     dist, site = tmp_path / "dist", tmp_path / "site"
     r = subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "--no-index",
                         "-w", str(dist), repo], capture_output=True, text=True)
