@@ -112,7 +112,8 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_fwd_kernel(const __nv_bfloat16
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) ; dw += sum_rows dy * xhat.
 // A row is shared by the four warps of a half CTA (128 threads, MAXV vectors per thread, d <= 1024 * MAXV): x and
-// dy are read once into registers, the gain stays in registers across rows, the row's dot product is combined
+// dy are read once into registers, the gain is re-read from L1 (keeping it in registers too cost spills at two
+// CTAs per SM: 0.44 of the copy bandwidth against 0.65 with one), the row's dot product is combined
 // through shared memory with one 128-thread barrier, and each thread accumulates the gain gradient of its own
 // columns over all rows it sees. The per-CTA partial gain gradients go to `dw_part` (gridDim.x * 2 rows of d
 // floats) and a second kernel sums them: no atomics.
@@ -130,11 +131,9 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(const __nv_bfloat16
   const int gt = threadIdx.x & 127;   // thread inside the half
   const int gw = gt >> 5, lane = gt & 31;
   float dwacc[MAXV][8];
-  uint4 wv[MAXV];
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int v = 0; v < MAXV; ++v) {
-    const int i = gt + v * 128;
-    wv[v] = i < nv ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[v][e] = 0.f;
   }
@@ -155,10 +154,11 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(const __nv_bfloat16
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
+      const int i = gt + v * 128;
       float xf[8], gf[8], wf[8];
       unpack8(xv[v], xf);
       unpack8(gv[v], gf);
-      unpack8(wv[v], wf);
+      unpack8(i < nv ? wr[i] : make_uint4(0u, 0u, 0u, 0u), wf);
 #pragma unroll
       for (int e = 0; e < 8; ++e) dot += gf[e] * wf[e] * xf[e];
     }
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_kernel(const __nv_bfloat16
         float xf[8], gf[8], wf[8], o[8];
         unpack8(xv[v], xf);
         unpack8(gv[v], gf);
-        unpack8(wv[v], wf);
+        unpack8(wr[i], wf);
         if (rr) unpack8(rr[i], o);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
