@@ -129,6 +129,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--cache-layout", default="heads", choices=["rows", "heads"],
+                    help="decode: (B, S, 2, H, D) rows-major cache or (B, 2, H, S, D) heads-major cache")
     ap.add_argument("--mean-doc-len", type=int, default=0,
                     help="attention kernels: packed documents with geometric lengths of this mean (segment ids); "
                          "-1 = segment ids present but all equal")
@@ -199,9 +201,15 @@ def main(argv=None) -> int:
         from ..ops import decode as Dk
 
         B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
-        cache = torch.randn(B, S, 2, H, D, device=dev).bfloat16()
         q = torch.randn(B, 1, H, D, device=dev).bfloat16()
-        fn = lambda: Dk.decode_partial(q, cache[:, :, 0], cache[:, :, 1], q_pos0=S, k_pos0=0)
+        if args.cache_layout == "rows":
+            cache = torch.randn(B, S, 2, H, D, device=dev).bfloat16()
+            ck, cv = cache[:, :, 0], cache[:, :, 1]
+        else:  # every (kv, head) is one contiguous stream of S rows
+            cache = torch.randn(B, 2, H, S, D, device=dev).bfloat16()
+            ck, cv = cache[:, 0].permute(0, 2, 1, 3), cache[:, 1].permute(0, 2, 1, 3)
+        fn = lambda: Dk.decode_partial(q, ck, cv, q_pos0=S, k_pos0=0)
+        res["cache_layout"] = args.cache_layout
         flops = 4.0 * B * S * H * D
         bytes_ = 2.0 * B * S * H * D * 2
         res.update(shape=[B, S, H, D], splits=Dk.default_splits(S, B, H))
