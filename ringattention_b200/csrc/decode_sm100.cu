@@ -285,10 +285,13 @@ __global__ void decode_merge_kernel(const MergeParams p) {
   if (p.lse_out && d == 0) p.lse_out[row] = lse;
 }
 
-// Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to
-// cache row (*pos_ptr - k0) of this rank's (B, S_max, 2, H, D) shard if that position is local.
-__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ cache,
-                                 const long long* __restrict__ pos_ptr, long long k0, int S_max, int HD,
+// Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to cache row
+// (*pos_ptr - k0) of this rank's shard if that position is local. The cache is given as two (B, S_max, H, D) views
+// with element strides (batch, row, head), so any layout of the shard works: rows-major (B, S, 2, H, D) or
+// heads-major (B, 2, H, S, D), where every (k|v, head) is one contiguous stream for the decode kernel.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
+                                 __nv_bfloat16* __restrict__ vc, long long sb, long long ss, long long sh,
+                                 const long long* __restrict__ pos_ptr, long long k0, int S_max, int H, int D,
                                  int stripe_n, int stripe_rank, long long stripe_base, long long stripe_len0) {
   long long r = *pos_ptr - k0;
   if (stripe_n > 0) {  // striped layout: token i = pos - len0 belongs to rank i % n, row base + i / n
@@ -297,9 +300,16 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfl
   }
   if (r < 0 || r >= S_max) return;
   const int b = blockIdx.x;
-  const uint4* src = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(b) * 3 + 1) * HD);
-  uint4* dst = reinterpret_cast<uint4*>(cache + ((static_cast<long long>(b) * S_max + r) * 2) * HD);
-  for (int i = threadIdx.x; i < 2 * HD / 8; i += blockDim.x) dst[i] = src[i];
+  const int HD = H * D, vpr = D / 8;  // 16-byte vectors per head row
+  const uint4* src_k = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(b) * 3 + 1) * HD);
+  const uint4* src_v = reinterpret_cast<const uint4*>(qkv + (static_cast<long long>(b) * 3 + 2) * HD);
+  for (int i = threadIdx.x; i < HD / 8; i += blockDim.x) {
+    const int h = i / vpr, c = i - h * vpr;
+    const long long off = b * sb + r * ss + h * sh + c * 8;
+    if (!RA_IN_BOUNDS(r, 1, S_max, kTagDecodeCacheRow)) continue;
+    *reinterpret_cast<uint4*>(kc + off) = src_k[i];
+    *reinterpret_cast<uint4*>(vc + off) = src_v[i];
+  }
 }
 
 // state = {position, step}: advanced once per decoded token.
@@ -448,14 +458,18 @@ extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long 
   return check_launch("decode_merge_kernel");
 }
 
-extern "C" int ra_kv_append(const void* qkv, void* cache, const long long* pos_ptr, long long k0, int S_max,
-                            int B, int HD, int stripe_n, int stripe_rank, long long stripe_base,
-                            long long stripe_len0, void* stream) {
+extern "C" int ra_kv_append(const void* qkv, void* k_cache, void* v_cache, long long sb, long long ss, long long sh,
+                            const long long* pos_ptr, long long k0, int S_max, int B, int H, int D, int stripe_n,
+                            int stripe_rank, long long stripe_base, long long stripe_len0, void* stream) {
   using namespace ra::decode;
-  if (HD % 8 || B < 1 || !pos_ptr) { set_error("ra_kv_append: bad arguments"); return kHostBadArg; }
+  if (D % 8 || B < 1 || H < 1 || !pos_ptr || (sb % 8) || (ss % 8) || (sh % 8)) {
+    set_error("ra_kv_append: bad arguments");
+    return kHostBadArg;
+  }
   kv_append_kernel<<<B, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(cache), pos_ptr, k0, S_max, HD,
-      stripe_n, stripe_rank, stripe_base, stripe_len0);
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(k_cache),
+      static_cast<__nv_bfloat16*>(v_cache), sb, ss, sh, pos_ptr, k0, S_max, H, D, stripe_n, stripe_rank, stripe_base,
+      stripe_len0);
   return check_launch("kv_append_kernel");
 }
 

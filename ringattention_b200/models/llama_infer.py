@@ -65,8 +65,13 @@ class LlamaInference:
         # only rows of the chunk being prefilled need their true positions (causal rule inside the chunk).
         self.n_rows = 0                             # local rows written by prefill
         self.prefill_len = 0                        # positions covered by prefill
-        self.cache = [torch.zeros(batch, self.S_max, 2, self.H, self.D, device=self.device, dtype=torch.bfloat16)
-                      for _ in range(cfg.n_layers)]
+        # Heads-major storage (B, 2, H, S_max, D): the rows of one (k|v, head) are contiguous, so every CTA of the
+        # split-KV decode kernel streams one long run instead of 256-byte pieces 16 KB apart. The kernels see
+        # (B, S_max, H, D) views with strides; the flash kernel's tensor maps and the decode kernel take any strides.
+        self._cache = [torch.zeros(batch, 2, self.H, self.S_max, self.D, device=self.device, dtype=torch.bfloat16)
+                       for _ in range(cfg.n_layers)]
+        self.k_cache = [c[:, 0].permute(0, 2, 1, 3) for c in self._cache]   # (B, S_max, H, D) views
+        self.v_cache = [c[:, 1].permute(0, 2, 1, 3) for c in self._cache]
         self.length = 0                             # tokens in the cache (global)
         # [position, step] on the device: lets one recorded CUDA graph serve every decode step
         self.state = torch.zeros(2, dtype=torch.int64, device=self.device)
@@ -129,11 +134,12 @@ class LlamaInference:
             qkv = P.lin_fwd(h1, f"l{l}.wqkv")
             K.rope_(qkv.view(B, t, 3 * H, D)[:, :, :2 * H], mypos, cfg.rope_theta)
             qkv5 = qkv.view(B, t, 3, H, D)
-            c = self.cache[l]
-            c[:, n0:n0 + t].copy_(qkv5[:, :, 1:3])                           # own K/V slice stays local
+            kc, vc = self.k_cache[l], self.v_cache[l]
+            kc[:, n0:n0 + t].copy_(qkv5[:, :, 1])                            # own K/V slice stays local
+            vc[:, n0:n0 + t].copy_(qkv5[:, :, 2])
             q_all = self._gather_tokens(qkv5[:, :, 0].contiguous())          # (B, Tc, H, D)
             ms = MaskSpec(causal_block_size=cfg.causal_block_size, q_pos=Positions(pos0), k_pos=k_pos)
-            o_p, lse_p = flash.flash_fwd(q_all, c[:, :n0 + t, 0], c[:, :n0 + t, 1], ms, out_fp32=(N > 1))
+            o_p, lse_p = flash.flash_fwd(q_all, kc[:, :n0 + t], vc[:, :n0 + t], ms, out_fp32=(N > 1))
             if N == 1:
                 attn = o_p
             else:
@@ -189,9 +195,8 @@ class LlamaInference:
             h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
             qkv = K.linear_auto(h1, P.w(f"l{l}.wqkv"))
             K.rope_at_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], self.state, cfg.rope_theta)
-            K.kv_append(qkv, self.cache[l], self.state, stripe=stripe)
-            c = self.cache[l]
-            attn = Dk.ring_decode_attention(qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous(), c[:, :, 0], c[:, :, 1],
+            K.kv_append(qkv, self.k_cache[l], self.v_cache[l], self.state, stripe=stripe)
+            attn = Dk.ring_decode_attention(qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous(), self.k_cache[l], self.v_cache[l],
                                             None, self.axis, self.symm_ring, k_pos0=0, state=self.state,
                                             exchange=l, exchanges_per_step=cfg.n_layers, stripe=stripe)
             x = K.linear_auto(attn.reshape(B, d), P.w(f"l{l}.wo"), residual=x)

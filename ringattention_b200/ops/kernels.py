@@ -240,16 +240,17 @@ def rope_at_(x, pos_state, theta: float, offset: int = 0):
     return x
 
 
-def kv_append(qkv, cache, pos_state, k0: int = 0, stripe=None):
-    """Write the K/V rows of a one-token ``(B, 1, 3, H, D)`` qkv buffer into the ``(B, S_max, 2, H, D)``
-    cache shard when the position in ``pos_state[0]`` belongs to this rank: row ``pos - k0`` of a
-    contiguous shard, or, with ``stripe = (ranks, rank, prefilled rows, prefilled positions)``, row
-    ``rows + i // ranks`` on rank ``i % ranks`` for decoded token ``i = pos - positions``."""
-    B, S_max, two, H, D = cache.shape
-    assert cache.is_contiguous() and qkv.is_contiguous() and two == 2
+def kv_append(qkv, k_cache, v_cache, pos_state, k0: int = 0, stripe=None):
+    """Write the K/V rows of a one-token ``(B, 1, 3, H, D)`` qkv buffer into the cache shard, given as two
+    ``(B, S_max, H, D)`` views of any layout with equal strides, when the position in ``pos_state[0]`` belongs to
+    this rank: row ``pos - k0`` of a contiguous shard, or, with ``stripe = (ranks, rank, prefilled rows, prefilled
+    positions)``, row ``rows + i // ranks`` on rank ``i % ranks`` for decoded token ``i = pos - positions``."""
+    B, S_max, H, D = k_cache.shape
+    assert qkv.is_contiguous() and k_cache.stride() == v_cache.stride() and k_cache.stride(3) == 1
     sn, sr, sb, sl = stripe if stripe is not None else (0, 0, 0, 0)
-    _lib.call("ra_kv_append", ptr(qkv), ptr(cache), ptr(pos_state), c_ll(k0), S_max, B, H * D, int(sn), int(sr),
-              c_ll(sb), c_ll(sl), stream_ptr())
+    _lib.call("ra_kv_append", ptr(qkv), ptr(k_cache), ptr(v_cache), c_ll(k_cache.stride(0)), c_ll(k_cache.stride(1)),
+              c_ll(k_cache.stride(2)), ptr(pos_state), c_ll(k0), S_max, B, H, D, int(sn), int(sr), c_ll(sb), c_ll(sl),
+              stream_ptr())
 
 
 def decode_advance(state):
