@@ -249,7 +249,7 @@ def main() -> int:
     # ---- device-timed steps (inputs resident on the device; a different batch each step)
     dev_pool = []
     for tk, tg, _ in pool:
-        a, b = trainer.shard_batch(tk, tg)
+        a, b = trainer.shard_batch(tk, tg, seg)
         dev_pool.append((a.to(dev).contiguous(), b.to(dev).contiguous()))
     ctx = trainer.context(seg)
     sampler = ClockSampler(local)

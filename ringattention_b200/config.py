@@ -53,8 +53,9 @@ class BlockwiseKwargs:
     the softmax without 1/(1-p) rescaling (ringattention_jax.py:119-123,311-321).
     ``dropout_rng`` is an int seed or a ``torch.Generator`` (a seed is drawn from it).
     ``layout`` is an extension: ``"contiguous"`` (reference behaviour: rank r owns tokens
-    ``[r*c, (r+1)*c)``) or ``"zigzag"`` (rank r owns chunks r and 2N-1-r of 2N, which balances
-    causal work across the ring).
+    ``[r*c, (r+1)*c)``), ``"zigzag"`` (rank r owns chunks r and 2N-1-r of 2N, which balances
+    causal work across the ring) or ``"pairs:a0-b0,..."`` (an explicit pairing of the 2N half-chunks, e.g. the one
+    ``ops.reference.balanced_pairs`` derives from the document boundaries of a packed batch).
     """
 
     causal_block_size: Optional[int] = None
@@ -94,8 +95,8 @@ class BlockwiseKwargs:
             raise ValueError("chunk sizes must be positive")
         if not (0.0 <= float(self.attn_pdrop) < 1.0):
             raise ValueError("attn_pdrop must be in [0, 1)")
-        if self.layout not in ("contiguous", "zigzag"):
-            raise ValueError("layout must be 'contiguous' or 'zigzag'")
+        if self.layout not in ("contiguous", "zigzag") and not str(self.layout).startswith("pairs:"):
+            raise ValueError("layout must be 'contiguous', 'zigzag' or 'pairs:a0-b0,a1-b1,...'")
 
     @property
     def dropout_active(self) -> bool:
@@ -262,6 +263,7 @@ class TrainConfig:
     steps: int = 10
     seed: int = 0
     packed_mean_doc_len: int = 0  # >0: packed documents with geometric lengths (segment ids)
+    balance_documents: bool = True  # packed documents on a ring: pair the half-chunks by their attention work
     zero1: bool = True            # shard fp32 master weights and AdamW moments over the sp/dp replicas
     log_every: int = 1
     ckpt_dir: Optional[str] = None

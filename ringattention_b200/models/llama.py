@@ -87,14 +87,17 @@ class LlamaModel:
 
     # ------------------------------------------------------------------ context
     def make_context(self, B: int, S_local: int, rank: int = 0, world: int = 1, segment_ids=None,
-                     symm_ring=None, total_tokens: Optional[int] = None) -> StepContext:
+                     symm_ring=None, total_tokens: Optional[int] = None, layout: Optional[str] = None) -> StepContext:
+        """``layout`` overrides the configured token layout for this context (the trainer passes the pairing that
+        balances a packed batch)."""
+        layout = layout or self.cfg.layout
         kw = BlockwiseKwargs(causal_block_size=self.cfg.causal_block_size,
                              query_chunk_size=min(self.cfg.query_chunk_size, S_local),
                              key_chunk_size=min(self.cfg.key_chunk_size, S_local),
-                             layout=self.cfg.layout)
+                             layout=layout)
         plan = A.make_plan(rank, world, B, S_local, S_local, self.H, kw, segment_ids=segment_ids,
                            device=self.device)
-        pos = Positions.from_segments(shard_segments(rank, world, S_local, self.cfg.layout))
+        pos = Positions.from_segments(shard_segments(rank, world, S_local, layout))
         return StepContext(B=B, S=S_local, plan=plan, positions=pos, symm_ring=symm_ring,
                            total_tokens=total_tokens if total_tokens is not None else B * S_local * world)
 

@@ -33,28 +33,70 @@ _M32 = 0xFFFFFFFF
 # --------------------------------------------------------------------------------------------
 # positions / layouts
 # --------------------------------------------------------------------------------------------
+def layout_pairs(layout: str, world: int):
+    """The half-chunk pair ``(a, b)`` of every rank for a two-run layout, or ``None`` for the contiguous one.
+
+    The sequence is cut into ``2 * world`` half-chunks. ``"zigzag"`` gives rank r the half-chunks r and 2N-1-r
+    (equal causal work on every rank). ``"pairs:a0-b0,a1-b1,..."`` names the pairing explicitly: any perfect
+    matching of the half-chunks, e.g. one that balances the work of packed documents (``balanced_pairs``)."""
+    if layout == "contiguous" or world == 1:
+        return None
+    if layout == "zigzag":
+        return [(r, 2 * world - 1 - r) for r in range(world)]
+    if layout.startswith("pairs:"):
+        pairs = [tuple(int(x) for x in item.split("-")) for item in layout[len("pairs:"):].split(",")]
+        if len(pairs) != world or sorted(c for pr in pairs for c in pr) != list(range(2 * world)):
+            raise ValueError(f"layout {layout!r} is not a pairing of the {2 * world} half-chunks of {world} ranks")
+        return pairs
+    raise ValueError(f"unknown layout {layout!r}")
+
+
+def balanced_pairs(segment_ids: torch.Tensor, world: int) -> str:
+    """A ``"pairs:..."`` layout that balances the attention work of packed documents over the ring.
+
+    ``segment_ids`` is ``(B, S)`` with ids that change at document boundaries (the rows a ring works on). Under a
+    causal mask a token attends to the tokens of its own document up to itself, so the work of a half-chunk is
+    the sum over its tokens of (position - start of its document + 1). Half-chunks are sorted by work and the
+    heaviest is paired with the lightest, the second heaviest with the second lightest, and so on, which minimises
+    the largest pair. Without document boundaries the work grows with the position and the result is the zig-zag
+    pairing."""
+    B, S = segment_ids.shape
+    n = 2 * world
+    if S % n:
+        raise ValueError("sequence length must be divisible by 2 * ring size")
+    seg = segment_ids.to(torch.int64)
+    pos = torch.arange(S, device=seg.device).expand(B, S)
+    is_start = torch.ones_like(seg, dtype=torch.bool)
+    is_start[:, 1:] = seg[:, 1:] != seg[:, :-1]
+    start = torch.cummax(torch.where(is_start, pos, torch.zeros_like(pos)), dim=1).values
+    work = (pos - start + 1).double().view(B, n, S // n).sum(dim=(0, 2))
+    order = torch.argsort(work, stable=True).tolist()
+    pairs = [tuple(sorted((order[i], order[n - 1 - i]))) for i in range(world)]
+    pairs.sort()
+    return "pairs:" + ",".join(f"{a}-{b}" for a, b in pairs)
+
+
 def shard_positions(rank: int, world: int, local_len: int, layout: str = "contiguous",
                     device=None) -> torch.Tensor:
     """Global token positions held by ``rank`` (int64, ``local_len`` entries)."""
-    if layout == "contiguous" or world == 1:
+    pairs = layout_pairs(layout, world)
+    if pairs is None:
         return torch.arange(rank * local_len, (rank + 1) * local_len, device=device)
-    if layout == "zigzag":
-        if local_len % 2:
-            raise ValueError("zigzag layout needs an even local length")
-        h = local_len // 2
-        a = torch.arange(rank * h, (rank + 1) * h, device=device)
-        b0 = (2 * world - 1 - rank) * h
-        b = torch.arange(b0, b0 + h, device=device)
-        return torch.cat([a, b])
-    raise ValueError(f"unknown layout {layout!r}")
+    if local_len % 2:
+        raise ValueError("a two-run layout needs an even local length")
+    h = local_len // 2
+    a, b = pairs[rank]
+    return torch.cat([torch.arange(a * h, (a + 1) * h, device=device), torch.arange(b * h, (b + 1) * h, device=device)])
 
 
 def shard_segments(rank: int, world: int, local_len: int, layout: str = "contiguous"):
     """The shard as a list of ``(local_start, global_start, length)`` contiguous runs."""
-    if layout == "contiguous" or world == 1:
+    pairs = layout_pairs(layout, world)
+    if pairs is None:
         return [(0, rank * local_len, local_len)]
     h = local_len // 2
-    return [(0, rank * h, h), (h, (2 * world - 1 - rank) * h, h)]
+    a, b = pairs[rank]
+    return [(0, a * h, h), (h, b * h, h)]
 
 
 def to_layout(x: torch.Tensor, world: int, layout: str, dim: int = 1) -> torch.Tensor:

@@ -16,7 +16,7 @@ from .models.llama import LlamaModel, StepContext
 from .models.params import FlatParams
 from .ops import _lib
 from .ops import kernels as K
-from .ops.reference import shard_positions
+from .ops.reference import balanced_pairs, shard_positions
 from .parallel import gradsync
 from .parallel.mesh import DeviceMesh
 from .utils.tracing import phase
@@ -141,6 +141,7 @@ class Trainer:
         self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
         self._ctx_cache: Optional[StepContext] = None
         self._ctx_seg_key = None
+        self._layout, self._layout_key = None, None
 
     # ------------------------------------------------------------------ data
     def make_global_batch(self):
@@ -148,10 +149,23 @@ class Trainer:
         return synthetic_batch(self.cfg, self.tc.global_batch, self.tc.seq_len, self.gen,
                                self.tc.packed_mean_doc_len)
 
-    def shard_batch(self, tokens, targets):
+    def layout_for(self, segment_ids=None) -> str:
+        """Token layout of the ring for a batch: the configured one, or, for packed documents on a two-run layout
+        (``TrainConfig.balance_documents``), the pairing of half-chunks that balances the documents' attention work
+        over the ranks of this ring (``ops.reference.balanced_pairs``). All ranks of a ring see the same rows and
+        get the same answer."""
+        if segment_ids is None or self.sp == 1 or self.cfg.layout == "contiguous" or not self.tc.balance_documents:
+            return self.cfg.layout
+        key = (segment_ids.data_ptr(), tuple(segment_ids.shape), segment_ids._version)
+        if self._layout_key != key:
+            b0 = self.batch_index * self.B
+            self._layout, self._layout_key = balanced_pairs(segment_ids[b0:b0 + self.B], self.sp), key
+        return self._layout
+
+    def shard_batch(self, tokens, targets, segment_ids=None):
         """Slice this rank's rows (batch groups) and token positions (sp shard, layout-aware)."""
         b0 = self.batch_index * self.B
-        pos = shard_positions(self.sp_rank, self.sp, self.S, self.cfg.layout)
+        pos = shard_positions(self.sp_rank, self.sp, self.S, self.layout_for(segment_ids))
         return (tokens[b0:b0 + self.B].index_select(1, pos), targets[b0:b0 + self.B].index_select(1, pos))
 
     def h2d_bytes_per_step(self) -> int:
@@ -175,7 +189,7 @@ class Trainer:
                 self._attn_pairs = float((ln * (ln + 1) / 2).sum())
             self._ctx_cache = self.model.make_context(
                 self.B, self.S, self.sp_rank, self.sp, segment_ids=seg, symm_ring=self.symm_ring,
-                total_tokens=self.tc.global_batch * self.tc.seq_len)
+                total_tokens=self.tc.global_batch * self.tc.seq_len, layout=self.layout_for(segment_ids))
             self._ctx_seg_key = key
         return self._ctx_cache
 
@@ -257,7 +271,7 @@ class Trainer:
         """The end-to-end step a user calls: sharded inputs come from pinned host memory, the loss
         comes back to the host."""
         self.check_peers()
-        tok, tgt = self.shard_batch(tokens_cpu, targets_cpu)
+        tok, tgt = self.shard_batch(tokens_cpu, targets_cpu, segment_ids)
         self._tok_host.copy_(tok)
         self._tgt_host.copy_(tgt)
         self._tok_dev.copy_(self._tok_host, non_blocking=True)

@@ -199,7 +199,7 @@ def mesh_parity(rank, world, dev, mesh_text, label, packed=0):
         if not zero1:
             # ---- gradients of one batch, reduced over the mesh, against one device
             ref, P_ref, loss_ref = _reference_gradients("llama-tiny", 11, tokens, targets, seg, dev)
-            tok, tgt = tr.shard_batch(tokens, targets)
+            tok, tgt = tr.shard_batch(tokens, targets, seg)
             P = tr.model.params
             P.ensure_grads().zero_()
             loss_sum = tr.model.forward_backward(tok.to(dev).contiguous(), tgt.to(dev).contiguous(), tr.context(seg))

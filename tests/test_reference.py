@@ -184,3 +184,40 @@ def test_layout_roundtrip():
         if world > 1:
             pos = torch.cat([R.shard_positions(r, world, 64 // world, "zigzag") for r in range(world)])
             assert sorted(pos.tolist()) == list(range(64))
+
+
+def test_explicit_pair_layout_on_the_ring():
+    """Any pairing of the half-chunks is a valid layout: the ring against dense attention with a pairing that is
+    neither contiguous nor zig-zag, causal and with segment ids."""
+    _ring_case(4, "pairs:0-5,1-2,3-6,4-7", 1, seg=True, S=512, H=2, D=16, qc=64, dtype=torch.float64)
+    with pytest.raises(ValueError):
+        R.layout_pairs("pairs:0-1,1-2", 2)          # not a perfect matching
+    with pytest.raises(ValueError):
+        R.layout_pairs("pairs:0-1", 2)              # wrong number of pairs
+
+
+def test_balanced_pairs_for_packed_documents():
+    """Without document boundaries the balancing pairing is the zig-zag; with packed documents it lowers the
+    largest per-rank work below the zig-zag's."""
+    world, S = 4, 4096
+    ids = torch.zeros(2, S, dtype=torch.int32)
+    assert R.layout_pairs(R.balanced_pairs(ids, world), world) == R.layout_pairs("zigzag", world)
+
+    def rank_work(seg, layout):
+        pos = torch.arange(S).expand_as(seg)
+        start_flag = torch.ones_like(seg, dtype=torch.bool)
+        start_flag[:, 1:] = seg[:, 1:] != seg[:, :-1]
+        start = torch.cummax(torch.where(start_flag, pos, torch.zeros_like(pos)), 1).values
+        w = (pos - start + 1).double()
+        return [float(w.index_select(1, R.shard_positions(r, world, S // world, layout)).sum()) for r in range(world)]
+
+    g = torch.Generator().manual_seed(3)
+    worse = 0
+    for trial in range(8):
+        seg = torch.cumsum((torch.rand(1, S, generator=g) < 1 / 300.0).int(), 1).int()
+        lay = R.balanced_pairs(seg, world)
+        wb, wz = rank_work(seg, lay), rank_work(seg, "zigzag")
+        assert abs(sum(wb) - sum(wz)) < 1e-6 * sum(wz)      # the same total work, distributed differently
+        assert max(wb) <= max(wz) + 1e-9
+        worse += max(wb) < 0.97 * max(wz)
+    assert worse >= 4                                         # and usually clearly better
