@@ -5,6 +5,7 @@ greedy decoding. Reports prefill tokens/s, decode tokens/s and p50 per-token lat
     python infer.py --model llama-7b --context 131072 --new-tokens 64
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 infer.py \
         --model llama-7b --context 1048576 --chunk 32768 --new-tokens 256 --batch 1
+    ... --streams 4      # four decode streams that share the one cached context
 """
 from __future__ import annotations
 
@@ -25,6 +26,9 @@ def main() -> int:
     ap.add_argument("--chunk", type=int, default=32768)
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--streams", type=int, default=0,
+                    help="decode this many streams (<= 8) from ONE cached context (batch must be 1): the way a batch of "
+                         "long-context requests fits when distinct contexts do not")
     ap.add_argument("--layers", type=int, default=None, help="override layer count (debug)")
     args = ap.parse_args()
 
@@ -50,7 +54,8 @@ def main() -> int:
             print(json.dumps({"error": "KV cache does not fit", "kv_cache_gb_per_gpu": kv_gb,
                               "free_gb": free_gb, "batch": args.batch, "context": args.context}))
         return 0
-    eng = LlamaInference(cfg, max_context=max_ctx, batch=args.batch, device=dev, axis=mesh.axis("sp"))
+    eng = LlamaInference(cfg, max_context=max_ctx, batch=args.batch, device=dev, axis=mesh.axis("sp"),
+                         streams=args.streams, max_new_tokens=args.new_tokens + 8)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.batch, args.context), generator=g)
     gen, timing = eng.generate(prompt.to(dev), args.new_tokens, chunk=args.chunk)
@@ -66,7 +71,8 @@ def main() -> int:
             "model": args.model, "n_layers": cfg.n_layers, "n_gpus": world, "batch": args.batch,
             "context": args.context, "chunk": args.chunk, "new_tokens": args.new_tokens,
             "prefill_tokens_per_s": args.batch * args.context / float(t[0]),
-            "decode_tokens_per_s": args.batch * len(steady) / float(t[1]),
+            "decode_tokens_per_s": max(args.batch, args.streams) * len(steady) / float(t[1]),
+            "streams_sharing_the_context": args.streams,
             "decode_first_steps_ms": [round(x, 3) for x in lat[:3]],
             "decode_p50_ms": statistics.median(steady), "decode_p90_ms": sorted(steady)[int(0.9 * (len(steady) - 1))],
             "kv_cache_gb_per_gpu": kv_gb, "data": "random tokens, random-init weights", "dtype": "bf16"}))

@@ -282,7 +282,16 @@ __global__ void decode_merge_kernel(const MergeParams p) {
     else
       reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16(o);
   }
-  if (p.lse_out && d == 0) p.lse_out[row] = lse;
+  if (p.lse_out && d == 0) {
+    // like `out`: row (b, h, i) of a decode call goes to position (b, i, h), so that the merged values of calls with
+    // different (B, QL) splits of the same queries line up
+    long long li = row;
+    if (p.QL > 0) {
+      const int i = row % p.QL, h = (row / p.QL) % p.H, b = row / (p.QL * p.H);
+      li = (static_cast<long long>(b) * p.QL + i) * p.H + h;
+    }
+    p.lse_out[li] = lse;
+  }
 }
 
 // Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to cache row

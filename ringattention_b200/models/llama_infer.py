@@ -42,8 +42,16 @@ from .params import FlatParams
 class LlamaInference:
     def __init__(self, cfg: LlamaConfig, max_context: int, batch: int = 1, device="cuda", seed: int = 0,
                  axis: "AxisContext | str | None" = None, params: Optional[FlatParams] = None,
-                 symm_ring=None):
+                 symm_ring=None, streams: int = 0, max_new_tokens: int = 512):
+        """``streams > 0``: one cached context (``batch`` must be 1) shared by that many decode streams (at most
+        8). The prefix is prefilled once and read once per decoded step for all streams; every stream keeps the
+        K/V of its own decoded tokens in a small private tail (``max_new_tokens`` long, striped over the ranks).
+        This is how a batch of long-context requests fits when distinct contexts do not: four 1M-token contexts
+        of the 7B model would need 2 TiB of KV."""
         self.cfg = cfg
+        if streams and (batch != 1 or not 1 <= streams <= 8):
+            raise ValueError("shared-prefix decoding takes batch = 1 and 1..8 streams")
+        self.streams = int(streams)
         self.device = torch.device(device)
         self.axis = resolve_axis(axis)
         self.rank, self.world = self.axis.rank, self.axis.size
@@ -77,7 +85,14 @@ class LlamaInference:
         self.state = torch.zeros(2, dtype=torch.int64, device=self.device)
         self._graph = None
         self._xchg = 0                              # prefill exchanges so far (parity picks the peer-memory buffer)
-        self._tok_buf = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._tok_buf = torch.zeros(max(batch, self.streams), dtype=torch.int32, device=self.device)
+        if self.streams:
+            t_tail = (max_new_tokens + self.world - 1) // self.world + 1
+            self._tail = [torch.zeros(self.streams, 2, self.H, t_tail, self.D, device=self.device, dtype=torch.bfloat16)
+                          for _ in range(cfg.n_layers)]
+            self.k_tail = [c[:, 0].permute(0, 2, 1, 3) for c in self._tail]  # (streams, T, H, D) views
+            self.v_tail = [c[:, 1].permute(0, 2, 1, 3) for c in self._tail]
+            self._sp_work = [dict() for _ in range(cfg.n_layers)]
         self._logits_buf = None
 
     # ------------------------------------------------------------------ helpers
@@ -188,17 +203,26 @@ class LlamaInference:
         """All launches of one decode step. Every per-token scalar (position, valid cache rows, inbox
         slot, barrier count) is read from device memory, so the sequence can be graph-captured."""
         cfg, P = self.cfg, self.params
-        B, H, D, d = self.B, self.H, self.D, self.d
+        B, H, D, d = (self.streams or self.B), self.H, self.D, self.d
         stripe = (self.world, self.rank, self.n_rows, self.prefill_len)
+        tail_stripe = (self.world, self.rank, 0, self.prefill_len)
         x = K.embedding_fwd(tokens, P.w("embed"))
         for l in range(cfg.n_layers):
             h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
             qkv = K.linear_auto(h1, P.w(f"l{l}.wqkv"))
             K.rope_at_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], self.state, cfg.rope_theta)
-            K.kv_append(qkv, self.k_cache[l], self.v_cache[l], self.state, stripe=stripe)
-            attn = Dk.ring_decode_attention(qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous(), self.k_cache[l], self.v_cache[l],
-                                            None, self.axis, self.symm_ring, k_pos0=0, state=self.state,
-                                            exchange=l, exchanges_per_step=cfg.n_layers, stripe=stripe)
+            q = qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous()
+            if self.streams:  # shared prefix: the new K/V go to the streams' private tails
+                K.kv_append(qkv, self.k_tail[l], self.v_tail[l], self.state, stripe=tail_stripe)
+                attn = Dk.shared_prefix_decode_attention(
+                    q, self.k_cache[l], self.v_cache[l], self.n_rows, self.k_tail[l], self.v_tail[l], self.axis,
+                    self.symm_ring, state=self.state, stripe=tail_stripe, exchange=l,
+                    exchanges_per_step=cfg.n_layers, work=self._sp_work[l])
+            else:
+                K.kv_append(qkv, self.k_cache[l], self.v_cache[l], self.state, stripe=stripe)
+                attn = Dk.ring_decode_attention(q, self.k_cache[l], self.v_cache[l],
+                                                None, self.axis, self.symm_ring, k_pos0=0, state=self.state,
+                                                exchange=l, exchanges_per_step=cfg.n_layers, stripe=stripe)
             x = K.linear_auto(attn.reshape(B, d), P.w(f"l{l}.wo"), residual=x)
             h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
             gu = K.linear_auto(h2, P.w(f"l{l}.wgu"))
@@ -258,6 +282,8 @@ class LlamaInference:
         out: List[torch.Tensor] = []
         lat: List[float] = []
         nxt = logits.argmax(dim=-1)
+        if self.streams:  # the streams start from the `streams` most likely continuations of the shared prefix
+            nxt = logits[0].topk(self.streams).indices
         for i in range(new_tokens):
             out.append(nxt.clone())
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -169,3 +169,63 @@ def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: 
         merge_partials(io[:n_o].view(rows, world, D), il[:n_l].view(rows, world), H, QL, out=out,
                        in_slot=(n_o, n_l), **sk)
     return out[:, :ql]
+
+
+def shared_prefix_decode_attention(q, k_prefix, v_prefix, n_prefix: int, k_tail, v_tail, axis, symm_ring=None, *,
+                                   state: torch.Tensor, stripe: tuple, exchange: int = 0, exchanges_per_step: int = 1,
+                                   work: Optional[dict] = None):
+    """Decode attention of ``S`` streams that share one cached prefix and have private tails.
+
+    ``q (S, 1, H, D)``: one query per stream. ``k_prefix, v_prefix (1, rows, H, D)``: this rank's rows of the shared
+    context, of which ``n_prefix`` are valid. ``k_tail, v_tail (S, T, H, D)``: this rank's rows of every stream's
+    decoded tokens (striped over the ranks: ``stripe = (ranks, rank, 0, prefix positions)``; the number of valid
+    rows comes from the position in ``state[0]`` on the device). The prefix is streamed once for all streams (the
+    streams become the query rows of one split-KV call, at most 8), the tails are a second, tiny call; both are
+    merged per stream with log-sum-exp weights and then across the ranks like any decode step. Returns ``(S, 1, H,
+    D)`` in ``v``'s dtype, identical on every rank. ``work``: a dict that keeps the intermediate buffers between
+    calls (needed under CUDA-graph capture, where addresses must not change)."""
+    rank, world = axis.rank, axis.size
+    S, one, H, D = q.shape
+    assert one == 1 and S <= 8 and k_prefix.shape[0] == 1
+    dev = q.device
+    work = work if work is not None else {}
+    rows = S * H
+    if "o12" not in work:
+        work["o12"] = torch.empty(2, rows, D, device=dev, dtype=torch.float32)
+        work["l12"] = torch.empty(2, rows, device=dev, dtype=torch.float32)
+    o12, l12 = work["o12"], work["l12"]
+    # ---- shared prefix: the streams as query rows of one call (the cache is read once)
+    qp, _, QL = _pad_q(q.view(1, S, H, D))
+    o_p, lse_p = decode_partial(qp, k_prefix, v_prefix, n_valid=n_prefix, q_pos0=-1, k_pos0=0)
+    if QL == S:
+        merge_partials(o_p, lse_p, H, QL, out=o12[0].view(1, S, H, D), lse_out=l12[0])
+    else:  # padded query rows: merge into a padded buffer, keep the first S
+        if "pad_o" not in work:
+            work["pad_o"] = torch.empty(1, QL, H, D, device=dev, dtype=torch.float32)
+            work["pad_l"] = torch.empty(QL * H, device=dev, dtype=torch.float32)
+        merge_partials(o_p, lse_p, H, QL, out=work["pad_o"], lse_out=work["pad_l"])
+        o12[0].copy_(work["pad_o"][0, :S].reshape(rows, D))
+        l12[0].copy_(work["pad_l"][:rows])
+    # ---- private tails: one query per stream against its own rows on this rank
+    o_t, lse_t = decode_partial(q.contiguous(), k_tail, v_tail, q_pos0=-1, k_pos0=0, pos_ptr=state.data_ptr(),
+                                stripe=stripe, splits=1)
+    merge_partials(o_t, lse_t, H, 1, out=o12[1].view(S, 1, H, D), lse_out=l12[1])
+    # ---- the two partials of every (stream, head) row, then the ranks
+    o_rows, l_rows = o12.permute(1, 0, 2), l12.permute(1, 0)            # (rows, 2, D), (rows, 2) views
+    out = torch.empty(S, 1, H, D, device=dev, dtype=v_prefix.dtype)
+    if world == 1:
+        merge_partials(o_rows, l_rows, H, 0, out=out)
+        return out
+    if symm_ring is None:
+        raise RuntimeError("multi-rank decode needs a symmetric-memory ring")
+    inbox_o = symm_ring.buffer("decode_inbox_o", 2 * rows * world * D * 4)
+    inbox_l = symm_ring.buffer("decode_inbox_lse", 2 * rows * world * 4)
+    o_tab, l_tab = symm_ring.peer_ptr_table("decode_inbox_o"), symm_ring.peer_ptr_table("decode_inbox_lse")
+    n_o, n_l = rows * world * D, rows * world
+    io, il = inbox_o.local.view(torch.float32), inbox_l.local.view(torch.float32)
+    sk = dict(step_ptr=state.data_ptr() + 8, slot_mul=exchanges_per_step, slot_add=exchange)
+    merge_partials(o_rows, l_rows, H, 0, inbox=(o_tab.data_ptr(), l_tab.data_ptr(), world, rank),
+                   out_slot=(n_o, n_l), **sk)
+    symm_ring.barrier()
+    merge_partials(io[:n_o].view(rows, world, D), il[:n_l].view(rows, world), H, 0, out=out, in_slot=(n_o, n_l), **sk)
+    return out

@@ -142,6 +142,19 @@ def decode_engine(rank, world, dev):
         tok = lb.argmax(dim=-1)
     ok &= worst < 0.03
     print(f"[{rank}] decode logits, 6 teacher-forced steps: worst rel {worst:.4f}", flush=True)
+    # three streams on one shared context (striped over the ring), private tails dealt round-robin to the ranks
+    sh = LlamaInference(cfg, max_context=8 * chunk, batch=1, seed=5, axis="sp", streams=3, max_new_tokens=16)
+    sh1 = LlamaInference(cfg, max_context=8 * chunk, batch=1, seed=5, axis=None, streams=3, max_new_tokens=16)
+    for c0 in range(0, prompt.shape[1], chunk):
+        la, lb = sh.prefill_chunk(prompt[:, c0:c0 + chunk]), sh1.prefill_chunk(prompt[:, c0:c0 + chunk])
+    tok = lb[0].topk(3).indices
+    worst = 0.0
+    for _ in range(2 * world + 1):
+        la, lb = sh.decode_step(tok), sh1.decode_step(tok)
+        worst = max(worst, rel(la, lb))
+        tok = lb.argmax(dim=-1)
+    ok &= worst < 0.03
+    print(f"[{rank}] shared-prefix decode, 3 streams: worst rel {worst:.4f}", flush=True)
     torch.cuda.synchronize()
     _lib.check_status()
     return ok

