@@ -38,6 +38,8 @@ def main() -> int:
     ap.add_argument("--log", default=None, help="append JSON lines to this file")
     ap.add_argument("--new-batch-every-step", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help="override the number of layers")
+    ap.add_argument("--no-balance", action="store_true",
+                    help="packed documents: keep the plain zig-zag pairing instead of the one that balances the documents")
     ap.add_argument("--phase-times", action="store_true",
                     help="log device milliseconds per phase (attention, linear layers, reductions) each step")
     args = ap.parse_args()
@@ -53,7 +55,8 @@ def main() -> int:
     cfg = LlamaConfig.named(args.model, layout=args.layout, remat=args.remat, **over)
     tc = TrainConfig(model=args.model, mesh=args.mesh, seq_len=args.seq_len, global_batch=args.global_batch,
                      lr=args.lr, steps=args.steps, packed_mean_doc_len=args.packed_mean_doc_len,
-                     ckpt_dir=args.ckpt_dir, ckpt_every=args.ckpt_every, resume=args.resume)
+                     ckpt_dir=args.ckpt_dir, ckpt_every=args.ckpt_every, resume=args.resume,
+                     balance_documents=not args.no_balance)
     tr = Trainer(cfg, tc)
     log = MetricsLogger(args.log, rank=tr.rank)
     if args.resume and args.ckpt_dir:
