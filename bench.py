@@ -311,7 +311,8 @@ def main() -> int:
             "loss": loss,
             "config": {"model": args.model, "n_layers": cfg.n_layers, "global_batch": global_batch,
                        "seq_len": seq_len, "parallelism": MeshConfig.parse(mesh).describe(),
-                       "layout": cfg.layout, "remat": cfg.remat, "optimizer": "AdamW fp32 master",
+                       "layout": cfg.layout, "remat": cfg.remat,
+                       "optimizer": "AdamW fp32 master" + (", state sharded over the ring" if trainer.zero is not None else ""),
                        "l2": "working set (13.5 GB bf16 weights + activations) far exceeds the 126 MB L2; no flush needed",
                        "ffn_chunk": cfg.ffn_chunk_size, "loss_chunk": cfg.loss_chunk_size},
             "clocks": clocks,
