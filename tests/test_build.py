@@ -32,8 +32,11 @@ def test_wheel_is_self_contained(tmp_path):
     # build from a copy, so that setuptools leaves its build/ and egg-info directories outside the repository
     # (the object files travel with the copy: nothing is recompiled)
     repo = str(tmp_path / "src")
-    shutil.copytree(src, repo, ignore=shutil.ignore_patterns(".git", "_work", "gpurun_out", "baseline", "profiles",
-                                                             "__pycache__", ".pytest_cache", "build", "*.egg-info"))
+    os.makedirs(repo)
+    shutil.copytree(os.path.join(src, "ringattention_b200"), os.path.join(repo, "ringattention_b200"),
+                    ignore=shutil.ignore_patterns("__pycache__"))
+    for f in ("pyproject.toml", "setup.py", "README.md"):
+        shutil.copy(os.path.join(src, f), repo)
     dist, site = tmp_path / "dist", tmp_path / "site"
     r = subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "--no-index",
                         "-w", str(dist), repo], capture_output=True, text=True)
