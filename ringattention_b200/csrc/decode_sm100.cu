@@ -18,6 +18,7 @@
 
 #include "common/bounds.cuh"
 #include "common/host_util.h"
+#include "common/sm100.cuh"
 
 RA_BOUNDS_TRANSLATION_UNIT()
 
@@ -64,6 +65,14 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
+}
+
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
 }
 
 // D = head dim (64 or 128), QL = query rows held per CTA.
@@ -294,6 +303,112 @@ __global__ void decode_merge_kernel(const MergeParams p) {
   }
 }
 
+// The whole cross-GPU merge of a decode step in one launch: merge this GPU's split partials of a row, store the
+// result into slot `my_rank` of every rank's inbox (peer stores), tell every rank that this row has arrived, wait
+// until the same row of every rank has arrived here, and merge those. Synchronisation is per row: CTA `row` of
+// rank a only ever waits for CTA `row` of the other ranks, and every CTA signals before it waits, so the launch
+// cannot deadlock as long as all its CTAs are resident at once (the launcher refuses larger grids). The wait is
+// bounded: after `timeout_ns` the CTA records kTimeoutPeerFlag in the status word and finishes with what is there.
+//   epoch    = *epoch_ptr + 1: counts the launches of this kernel on the ring (same on every rank); the last CTA to
+//              finish stores it back, so a launch recorded in a CUDA graph works on every replay
+//   slot     = epoch & 1: the inbox is double-buffered. A rank can be at most one exchange ahead of another (it
+//              needs that rank's flag of the previous exchange to get further), so two slots are enough
+//   flags[r] = rank r's (max_rows, n_ranks) words; word (row, src) holds the last epoch whose row `row` from
+//              rank `src` is complete in r's inbox
+struct ExchangeParams {
+  MergeParams m;  // stage 1 inputs, inbox pointer tables, ranks, final `out` and its row mapping
+  uint32_t* const* flags;
+  uint32_t* epoch_ptr;
+  unsigned int* done_ctr;
+  const float* inbox_o_local;  // this rank's inbox: 2 slots of (rows, n_ranks, D) / (rows, n_ranks)
+  const float* inbox_l_local;
+  long long slot_rows;  // rows per inbox slot (the same for every launch on the ring, whatever its own row count)
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__global__ void decode_merge_exchange_kernel(const ExchangeParams e) {
+  const MergeParams& p = e.m;
+  const int row = blockIdx.x, d = threadIdx.x, n = p.n_ranks;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(e.epoch_ptr) + 1u;
+  const long long slot = epoch & 1u;
+  // ---- stage 1: this GPU's splits
+  const float* lp = p.lse_part + static_cast<long long>(row) * p.l_rs;
+  float mx = -INFINITY;
+  for (int s = 0; s < p.nparts; ++s) mx = fmaxf(mx, lp[s * p.l_ps]);
+  float wsum = 0.f, o = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < p.nparts; ++s) {
+      const float w = __expf(lp[s * p.l_ps] - mx);
+      wsum += w;
+      o += w * p.o_part[static_cast<long long>(row) * p.o_rs + s * p.o_ps + d];
+    }
+    o /= wsum;
+  }
+  const float lse = mx == -INFINITY ? -INFINITY : mx + __logf(wsum);
+  const long long slot_o = slot * e.slot_rows * n * p.D, slot_l = slot * e.slot_rows * n;
+  for (int r = 0; r < n; ++r) {
+    p.inbox_o[r][slot_o + (static_cast<long long>(row) * n + p.my_rank) * p.D + d] = o;
+    if (d == 0) p.inbox_lse[r][slot_l + static_cast<long long>(row) * n + p.my_rank] = lse;
+  }
+  __threadfence_system();
+  __syncthreads();
+  // ---- signal every rank, then wait for every rank's copy of this row
+  if (d < n) {
+    uint32_t* remote = e.flags[d] + static_cast<long long>(row) * n + p.my_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const uint32_t* mine = e.flags[p.my_rank] + static_cast<long long>(row) * n + d;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) break;
+      if (((++it) & 255u) == 0u && globaltimer_ns() - t0 > e.timeout_ns) {
+        if (e.status) atomicCAS(e.status, 0, static_cast<int>(kTimeoutPeerFlag));
+        break;
+      }
+      __nanosleep(100);
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  // ---- stage 2: the ranks' partials of this row (written by peers: read past L1)
+  const float* il = e.inbox_l_local + slot_l + static_cast<long long>(row) * n;
+  const float* io = e.inbox_o_local + slot_o + static_cast<long long>(row) * n * p.D;
+  mx = -INFINITY;
+  for (int r = 0; r < n; ++r) mx = fmaxf(mx, __ldcg(il + r));
+  wsum = 0.f;
+  o = 0.f;
+  if (mx != -INFINITY) {
+    for (int r = 0; r < n; ++r) {
+      const float w = __expf(__ldcg(il + r) - mx);
+      wsum += w;
+      o += w * __ldcg(io + static_cast<long long>(r) * p.D + d);
+    }
+    o /= wsum;
+  }
+  long long oi = static_cast<long long>(row) * p.D + d;
+  if (p.QL > 0) {  // row = (b*H + h)*QL + i  ->  out[b, i, h, d]
+    const int i = row % p.QL, h = (row / p.QL) % p.H, b = row / (p.QL * p.H);
+    oi = ((static_cast<long long>(b) * p.QL + i) * p.H + h) * p.D + d;
+  }
+  if (!RA_IN_BOUNDS(oi, 1, static_cast<long long>(gridDim.x) * p.D, kTagDecodeMerge)) {
+  } else if (p.out_fp32)
+    reinterpret_cast<float*>(p.out)[oi] = o;
+  else
+    reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16(o);
+  // ---- the last CTA to get here advances the ring's launch counter
+  __syncthreads();
+  if (d == 0) {
+    const unsigned int prev = atomicAdd(e.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *e.done_ctr = 0u;
+      *reinterpret_cast<volatile uint32_t*>(e.epoch_ptr) = epoch;
+    }
+  }
+}
+
 // Decode-time cache append: the new token's K and V (rows of a (B, 1, 3, H, D) qkv buffer) go to cache row
 // (*pos_ptr - k0) of this rank's shard if that position is local. The cache is given as two (B, S_max, H, D) views
 // with element strides (batch, row, head), so any layout of the shard works: rows-major (B, S, 2, H, D) or
@@ -370,7 +485,197 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16
     if (lane == 0) {
       float v = acc[m];
       if (res) v += __bfloat162float(res[static_cast<long long>(m) * N + warp]);
-      y[static_cast<long long>(m) * N + warp] = __float2bfloat16(v);
+      if (RA_IN_BOUNDS(warp, 1, N, kTagSmallMLinear)) y[static_cast<long long>(m) * N + warp] = __float2bfloat16(v);
+    }
+  }
+}
+
+// The same product with a prologue f applied to x, so that a decode step needs no separate normalisation or
+// activation launch: y = f(x) W^T (+ res).
+//   PRO_RMSNORM  f(x) = x * rsqrt(mean(x^2) + eps) * gain     (x is the (M, K) residual stream)
+//   PRO_SWIGLU   f(x) = silu(x[:, :K]) * x[:, K:]              (x is the (M, 2K) gate/up projection)
+// f(x) is built ONCE per CTA in shared memory (M * K bf16) and every warp then walks `cpw` consecutive columns
+// against it; the launcher picks cpw so that the whole grid is resident at once. Each warp issues the first
+// weight loads of its first column before the prologue, so the prologue's latency hides behind them. (Applying
+// f inside every warp's k loop instead repeats it N times and made a 7B decode step 9 % slower.)
+enum { PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
+
+template <int M, int PRO>
+__global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ w,
+                                                                  __nv_bfloat16* __restrict__ y,
+                                                                  const __nv_bfloat16* __restrict__ res,
+                                                                  const __nv_bfloat16* __restrict__ gain, float eps,
+                                                                  int N, int K, int cpw) {
+  extern __shared__ uint4 xs[];  // [M][K / 8] f(x) as bf16, without the rstd factor of RMSNorm
+  __shared__ float red[8][M];
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+  const int n16 = K / 8;
+  const int col0 = (blockIdx.x * 8 + wid) * cpw;
+  const bool full = n16 >= 128;  // the unrolled loop runs at least once
+  const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(col0 < N ? col0 : 0) * K);
+  uint4 w0 = {}, w1 = {}, w2 = {}, w3 = {};
+  if (full && col0 < N) {
+    w0 = wr[lane];
+    w1 = wr[lane + 32];
+    w2 = wr[lane + 64];
+    w3 = wr[lane + 96];
+  }
+  // ---- prologue: f(x) -> shared memory
+  float ss[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    ss[m] = 0.f;
+    const long long ldx = PRO == PRO_SWIGLU ? 2ll * K : K;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + m * ldx);
+    for (int c = tid; c < n16; c += 256) {
+      float xf[8], of[8];
+      unpack8(xr[c], xf);
+      unpack8(PRO == PRO_SWIGLU ? xr[c + n16] : reinterpret_cast<const uint4*>(gain)[c], of);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (PRO == PRO_RMSNORM) {
+          ss[m] = fmaf(xf[e], xf[e], ss[m]);
+          xf[e] *= of[e];
+        } else {
+          xf[e] = xf[e] / (1.f + __expf(-xf[e])) * of[e];  // same arithmetic as the stand-alone activation kernel
+        }
+      }
+      xs[m * n16 + c] = pack8(xf);
+    }
+  }
+  float rstd[M];
+  if (PRO == PRO_RMSNORM) {
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+      if (lane == 0) red[wid][m] = ss[m];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    rstd[m] = 1.f;
+    if (PRO == PRO_RMSNORM) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t += red[i][m];
+      rstd[m] = rsqrtf(t / K + eps);
+    }
+  }
+  // ---- cpw columns per warp
+  for (int j = 0; j < cpw; ++j) {
+    const int col = col0 + j;
+    if (col >= N) break;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    auto consume = [&](const uint4& wv, int c) {
+      float wf[8];
+      unpack8(wv, wf);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float xf[8];
+        unpack8(xs[m * n16 + c], xf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+      }
+    };
+    int c = lane;
+    if (full) {
+      if (j > 0) {
+        w0 = wr[c];
+        w1 = wr[c + 32];
+        w2 = wr[c + 64];
+        w3 = wr[c + 96];
+      }
+      while (true) {
+        const int cn = c + 128;
+        const bool more = cn + 96 < n16;
+        uint4 n0 = {}, n1 = {}, n2 = {}, n3 = {};
+        if (more) {  // the next four loads leave before this group is consumed
+          n0 = wr[cn];
+          n1 = wr[cn + 32];
+          n2 = wr[cn + 64];
+          n3 = wr[cn + 96];
+        }
+        consume(w0, c);
+        consume(w1, c + 32);
+        consume(w2, c + 64);
+        consume(w3, c + 96);
+        c = cn;
+        if (!more) break;
+        w0 = n0;
+        w1 = n1;
+        w2 = n2;
+        w3 = n3;
+      }
+    }
+    for (; c < n16; c += 32) consume(wr[c], c);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+      if (lane == 0) {
+        float v = acc[m] * rstd[m];
+        if (res) v += __bfloat162float(res[static_cast<long long>(m) * N + col]);
+        if (RA_IN_BOUNDS(col, 1, N, kTagSmallMLinear)) y[static_cast<long long>(m) * N + col] = __float2bfloat16(v);
+      }
+    }
+    wr += n16;
+  }
+}
+
+// One decode token per sequence: rotate the q and k heads of the (B, 1, 3, H, D) qkv buffer in place (RoPE at the
+// position in *pos_ptr) and append the rotated K and the V to the cache shard when this rank owns the position
+// (same ownership rule and cache views as kv_append_kernel). One launch instead of two per layer and token.
+template <int D>
+__global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
+                                   __nv_bfloat16* __restrict__ vc, long long sb, long long ss, long long sh,
+                                   const long long* __restrict__ pos_ptr, float log2_theta, long long k0, int S_max,
+                                   int H, int stripe_n, int stripe_rank, long long stripe_base,
+                                   long long stripe_len0) {
+  const long long pos = *pos_ptr;
+  long long r = pos - k0;
+  if (stripe_n > 0) {
+    const long long i = pos - stripe_len0;
+    r = (i >= 0 && i % stripe_n == stripe_rank) ? stripe_base + i / stripe_n : -1;
+  }
+  const bool mine = r >= 0 && r < S_max;
+  const int b = blockIdx.x;
+  constexpr int hd2 = D / 2, VPH = hd2 / 8;  // 16-byte vectors per half head
+  __nv_bfloat16* base = qkv + static_cast<long long>(b) * 3 * H * D;
+  // q and k heads: 2H heads x VPH vector pairs
+  for (int i = threadIdx.x; i < 2 * H * VPH; i += blockDim.x) {
+    const int hh = i / VPH, v = i - hh * VPH;  // hh in [0, 2H): q heads then k heads
+    __nv_bfloat16* p = base + static_cast<long long>(hh) * D + v * 8;
+    float a[8], c[8];
+    unpack8(*reinterpret_cast<const uint4*>(p), a);
+    unpack8(*reinterpret_cast<const uint4*>(p + hd2), c);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float inv_freq = exp2f(-log2_theta * (2.0f * (v * 8 + e) / D));
+      float sn, cs;
+      sincosf(static_cast<int>(pos) * inv_freq, &sn, &cs);  // same arithmetic as the stand-alone RoPE kernel
+      const float a2 = a[e] * cs - c[e] * sn, c2 = c[e] * cs + a[e] * sn;
+      a[e] = a2;
+      c[e] = c2;
+    }
+    const uint4 lo = pack8(a), hi = pack8(c);
+    *reinterpret_cast<uint4*>(p) = lo;
+    *reinterpret_cast<uint4*>(p + hd2) = hi;
+    if (mine && hh >= H && RA_IN_BOUNDS(r, 1, S_max, kTagDecodeCacheRow)) {
+      const long long off = b * sb + r * ss + (hh - H) * sh + v * 8;
+      *reinterpret_cast<uint4*>(kc + off) = lo;
+      *reinterpret_cast<uint4*>(kc + off + hd2) = hi;
+    }
+  }
+  if (mine) {
+    const uint4* src_v = reinterpret_cast<const uint4*>(base + 2ll * H * D);
+    for (int i = threadIdx.x; i < H * D / 8; i += blockDim.x) {
+      const int h = i / (D / 8), cidx = i - h * (D / 8);
+      *reinterpret_cast<uint4*>(vc + b * sb + r * ss + h * sh + cidx * 8) = src_v[i];
     }
   }
 }
@@ -467,6 +772,48 @@ extern "C" int ra_decode_merge(const float* o_part, const float* lse_part, long 
   return check_launch("decode_merge_kernel");
 }
 
+// Rows one launch of the fused exchange may have: every CTA has to be resident while it waits for its peers.
+extern "C" int ra_decode_exchange_max_rows() { return 2 * sm_count(); }
+
+// `sync` : this rank's 8-byte {epoch, done counter} words (zero-initialised, used by this kernel only).
+// `flags`: device table of every rank's flag words, each (>= rows * n_ranks) u32, zero-initialised.
+// `inbox_o` / `inbox_lse`: device tables of every rank's inbox, 2 slots of (slot_rows, n_ranks, D) and (slot_rows,
+// n_ranks) floats; `*_local` this rank's own. Launches with different row counts may share them: the slot stride
+// does not depend on `rows`.
+extern "C" int ra_decode_merge_exchange(const float* o_part, const float* lse_part, long long o_rs, long long o_ps,
+                                        long long l_rs, long long l_ps, int rows, int nparts, int D, int H, int QL,
+                                        void* out, int out_fp32, void* const* inbox_o, void* const* inbox_lse,
+                                        const float* inbox_o_local, const float* inbox_l_local, int slot_rows,
+                                        void* const* flags, void* sync, int n_ranks, int my_rank, unsigned long long timeout_ns,
+                                        int* status, void* stream) {
+  using namespace ra::decode;
+  if (rows < 1 || rows > ra_decode_exchange_max_rows() || nparts < 1 || (D != 64 && D != 128) || n_ranks < 2 ||
+      n_ranks > 32 || my_rank < 0 || my_rank >= n_ranks || !out || !flags || !sync || slot_rows < rows) {
+    set_error("ra_decode_merge_exchange: bad shape (rows must not exceed twice the SM count)");
+    return kHostBadArg;
+  }
+  ExchangeParams e;
+  MergeParams& p = e.m;
+  p = MergeParams{};
+  p.o_part = o_part; p.lse_part = lse_part;
+  p.o_rs = o_rs; p.o_ps = o_ps; p.l_rs = l_rs; p.l_ps = l_ps;
+  p.rows = rows; p.nparts = nparts; p.D = D; p.H = H; p.QL = QL;
+  p.out = out; p.out_fp32 = out_fp32;
+  p.inbox_o = reinterpret_cast<float* const*>(inbox_o);
+  p.inbox_lse = reinterpret_cast<float* const*>(inbox_lse);
+  p.n_ranks = n_ranks; p.my_rank = my_rank;
+  e.flags = reinterpret_cast<uint32_t* const*>(flags);
+  e.epoch_ptr = static_cast<uint32_t*>(sync);
+  e.done_ctr = static_cast<unsigned int*>(sync) + 1;
+  e.inbox_o_local = inbox_o_local;
+  e.inbox_l_local = inbox_l_local;
+  e.slot_rows = slot_rows;
+  e.timeout_ns = timeout_ns;
+  e.status = status;
+  decode_merge_exchange_kernel<<<rows, D, 0, static_cast<cudaStream_t>(stream)>>>(e);
+  return check_launch("decode_merge_exchange_kernel");
+}
+
 extern "C" int ra_kv_append(const void* qkv, void* k_cache, void* v_cache, long long sb, long long ss, long long sh,
                             const long long* pos_ptr, long long k0, int S_max, int B, int H, int D, int stripe_n,
                             int stripe_rank, long long stripe_base, long long stripe_len0, void* stream) {
@@ -511,4 +858,64 @@ extern "C" int ra_small_m_linear(const void* x, const void* w, void* y, const vo
     default: small_m_linear_kernel<8><<<blocks, 256, 0, s>>>(xx, ww, yy, rr, N, K); break;
   }
   return check_launch("small_m_linear_kernel");
+}
+
+// Shared memory the prologue variant needs: M * K bf16. The Python side falls back to two launches above this.
+extern "C" int ra_small_m_linear_fused_max_smem() { return 48 * 1024; }
+
+extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, const void* res, const void* gain,
+                                       float eps, int prologue, int M, int N, int K, void* stream) {
+  using namespace ra::decode;
+  const long long smem = static_cast<long long>(M) * K * 2;
+  if (M < 1 || M > 8 || K % 8 || N < 1 || (prologue != PRO_RMSNORM && prologue != PRO_SWIGLU) ||
+      (prologue == PRO_RMSNORM && !gain) || smem > ra_small_m_linear_fused_max_smem()) {
+    set_error("ra_small_m_linear_fused: need 1 <= M <= 8, K % 8 == 0, M * K * 2 <= 48 KB, a prologue of 1 (RMSNorm, "
+              "with a gain) or 2 (SwiGLU)");
+    return kHostBadArg;
+  }
+  // columns per warp: the whole grid resident at once (four CTAs of 256 threads per SM)
+  const int resident = sm_count() * 4;
+  int cpw = (N + 8 * resident - 1) / (8 * resident);
+  if (cpw < 1) cpw = 1;
+  const int blocks = (N + 8 * cpw - 1) / (8 * cpw);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
+  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
+  const __nv_bfloat16* gg = static_cast<const __nv_bfloat16*>(gain);
+#define RA_SML_CASE(MM)                                                                                        \
+  case MM:                                                                                                     \
+    if (prologue == PRO_RMSNORM)                                                                               \
+      small_m_linear_pro_kernel<MM, PRO_RMSNORM><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw); \
+    else                                                                                                       \
+      small_m_linear_pro_kernel<MM, PRO_SWIGLU><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw);  \
+    break;
+  switch (M) {
+    RA_SML_CASE(1) RA_SML_CASE(2) RA_SML_CASE(3) RA_SML_CASE(4) RA_SML_CASE(5) RA_SML_CASE(6) RA_SML_CASE(7)
+    RA_SML_CASE(8)
+  }
+#undef RA_SML_CASE
+  return check_launch("small_m_linear_pro_kernel");
+}
+
+extern "C" int ra_rope_append(void* qkv, void* k_cache, void* v_cache, long long sb, long long ss, long long sh,
+                              const long long* pos_ptr, float theta, long long k0, int S_max, int B, int H, int D,
+                              int stripe_n, int stripe_rank, long long stripe_base, long long stripe_len0,
+                              void* stream) {
+  using namespace ra::decode;
+  if ((D != 64 && D != 128) || B < 1 || H < 1 || !pos_ptr || (sb % 8) || (ss % 8) || (sh % 8)) {
+    set_error("ra_rope_append: bad arguments");
+    return kHostBadArg;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16 *q = static_cast<__nv_bfloat16*>(qkv), *kc = static_cast<__nv_bfloat16*>(k_cache),
+                *vc = static_cast<__nv_bfloat16*>(v_cache);
+  if (D == 128)
+    rope_append_kernel<128><<<B, 256, 0, s>>>(q, kc, vc, sb, ss, sh, pos_ptr, log2f(theta), k0, S_max, H, stripe_n,
+                                              stripe_rank, stripe_base, stripe_len0);
+  else
+    rope_append_kernel<64><<<B, 256, 0, s>>>(q, kc, vc, sb, ss, sh, pos_ptr, log2f(theta), k0, S_max, H, stripe_n,
+                                             stripe_rank, stripe_base, stripe_len0);
+  return check_launch("rope_append_kernel");
 }

@@ -208,27 +208,25 @@ class LlamaInference:
         tail_stripe = (self.world, self.rank, 0, self.prefill_len)
         x = K.embedding_fwd(tokens, P.w("embed"))
         for l in range(cfg.n_layers):
-            h1, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n1"), cfg.rms_eps)
-            qkv = K.linear_auto(h1, P.w(f"l{l}.wqkv"))
-            K.rope_at_(qkv.view(B, 1, 3 * H, D)[:, :, :2 * H], self.state, cfg.rope_theta)
-            q = qkv.view(B, 1, 3, H, D)[:, :, 0].contiguous()
+            # RMSNorm runs in the prologue of the projection, RoPE and the cache append share a launch, and
+            # SwiGLU runs in the prologue of the down projection: 9 launches per layer instead of 13
+            qkv = K.norm_linear(x, P.w(f"l{l}.n1"), cfg.rms_eps, P.w(f"l{l}.wqkv"))
+            q = qkv.view(B, 1, 3, H, D)[:, :, 0]
             if self.streams:  # shared prefix: the new K/V go to the streams' private tails
-                K.kv_append(qkv, self.k_tail[l], self.v_tail[l], self.state, stripe=tail_stripe)
+                K.rope_append(qkv, self.k_tail[l], self.v_tail[l], self.state, cfg.rope_theta, stripe=tail_stripe)
                 attn = Dk.shared_prefix_decode_attention(
-                    q, self.k_cache[l], self.v_cache[l], self.n_rows, self.k_tail[l], self.v_tail[l], self.axis,
-                    self.symm_ring, state=self.state, stripe=tail_stripe, exchange=l,
+                    q.contiguous(), self.k_cache[l], self.v_cache[l], self.n_rows, self.k_tail[l], self.v_tail[l],
+                    self.axis, self.symm_ring, state=self.state, stripe=tail_stripe, exchange=l,
                     exchanges_per_step=cfg.n_layers, work=self._sp_work[l])
             else:
-                K.kv_append(qkv, self.k_cache[l], self.v_cache[l], self.state, stripe=stripe)
-                attn = Dk.ring_decode_attention(q, self.k_cache[l], self.v_cache[l],
+                K.rope_append(qkv, self.k_cache[l], self.v_cache[l], self.state, cfg.rope_theta, stripe=stripe)
+                attn = Dk.ring_decode_attention(q.contiguous(), self.k_cache[l], self.v_cache[l],
                                                 None, self.axis, self.symm_ring, k_pos0=0, state=self.state,
                                                 exchange=l, exchanges_per_step=cfg.n_layers, stripe=stripe)
             x = K.linear_auto(attn.reshape(B, d), P.w(f"l{l}.wo"), residual=x)
-            h2, _ = K.rmsnorm_fwd(x, P.w(f"l{l}.n2"), cfg.rms_eps)
-            gu = K.linear_auto(h2, P.w(f"l{l}.wgu"))
-            x = K.linear_auto(K.swiglu_fwd(gu), P.w(f"l{l}.wd"), residual=x)
-        hf, _ = K.rmsnorm_fwd(x, P.w("nf"), cfg.rms_eps)
-        logits = K.linear_auto(hf, P.w("lm_head")).float()
+            gu = K.norm_linear(x, P.w(f"l{l}.n2"), cfg.rms_eps, P.w(f"l{l}.wgu"))
+            x = K.swiglu_linear(gu, P.w(f"l{l}.wd"), residual=x)
+        logits = K.norm_linear(x, P.w("nf"), cfg.rms_eps, P.w("lm_head")).float()
         K.decode_advance(self.state)
         return logits
 

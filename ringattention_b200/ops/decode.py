@@ -111,6 +111,35 @@ def merge_partials(o_part, lse_part, H: int, QL: int, *, out=None, lse_out=None,
     return out
 
 
+def exchange_fits(rows: int) -> bool:
+    """Whether the one-launch cross-GPU merge takes this many (batch, head, query) rows: all its CTAs have to be
+    resident while they wait for their peers."""
+    return rows <= _lib.lib().ra_decode_exchange_max_rows()
+
+
+def merge_exchange(o_part, lse_part, H: int, QL: int, out, symm_ring) -> None:
+    """Merge the split partials of every row, exchange the result with the other ranks of ``symm_ring`` by peer
+    stores, wait per row for theirs and merge those into ``out``: one launch (no separate barrier, no second merge
+    kernel). Collective over the ring; every rank must call it with the same shapes in the same order."""
+    rows, nparts, D = o_part.shape
+    world, rank = symm_ring.size, symm_ring.rank
+    assert o_part.stride(2) == 1 and exchange_fits(rows)
+    max_rows = _lib.lib().ra_decode_exchange_max_rows()
+    box_o = symm_ring.buffer("decode_xchg_o", 2 * max_rows * world * D * 4)
+    box_l = symm_ring.buffer("decode_xchg_lse", 2 * max_rows * world * 4)
+    flags = symm_ring.buffer("decode_xchg_flags", max_rows * world * 4)
+    sync = symm_ring.scratch_zeros("decode_xchg_sync", 8)
+    _lib.call("ra_decode_merge_exchange", c_vp(o_part.data_ptr()), c_vp(lse_part.data_ptr()),
+              c_ll(o_part.stride(0)), c_ll(o_part.stride(1)), c_ll(lse_part.stride(0)), c_ll(lse_part.stride(1)),
+              rows, nparts, D, H, QL, c_vp(out.data_ptr()), int(out.dtype == torch.float32),
+              c_vp(symm_ring.peer_ptr_table("decode_xchg_o").data_ptr()),
+              c_vp(symm_ring.peer_ptr_table("decode_xchg_lse").data_ptr()),
+              c_vp(box_o.ptr), c_vp(box_l.ptr), max_rows,
+              c_vp(symm_ring.peer_ptr_table("decode_xchg_flags").data_ptr()),
+              c_vp(sync.data_ptr()), world, rank, ctypes.c_ulonglong(symm_ring.timeout_ns),
+              c_vp(_lib.status_tensor(o_part.device).data_ptr()), _lib.stream_ptr())
+
+
 def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: Optional[int] = None,
                           q_pos0: int = -1, k_pos0: Optional[int] = None, state: Optional[torch.Tensor] = None,
                           exchange: int = 0, exchanges_per_step: int = 1, stripe: Optional[tuple] = None):
@@ -144,6 +173,10 @@ def ring_decode_attention(q, k, v, attn_mask, axis, symm_ring=None, *, n_valid: 
     if symm_ring is None:
         raise RuntimeError("multi-rank decode needs a symmetric-memory ring")
     rows = B * H * QL
+    if exchange_fits(rows):
+        merge_exchange(o_part, lse_part, H, QL, out, symm_ring)
+        return out[:, :ql]
+    # too many rows for the one-launch exchange: merge into the inboxes, barrier, merge the ranks
     inbox_o = symm_ring.buffer("decode_inbox_o", 2 * rows * world * D * 4)
     inbox_l = symm_ring.buffer("decode_inbox_lse", 2 * rows * world * 4)
     o_tab, l_tab = symm_ring.peer_ptr_table("decode_inbox_o"), symm_ring.peer_ptr_table("decode_inbox_lse")
@@ -218,6 +251,9 @@ def shared_prefix_decode_attention(q, k_prefix, v_prefix, n_prefix: int, k_tail,
         return out
     if symm_ring is None:
         raise RuntimeError("multi-rank decode needs a symmetric-memory ring")
+    if exchange_fits(rows):
+        merge_exchange(o_rows, l_rows, H, 0, out, symm_ring)
+        return out
     inbox_o = symm_ring.buffer("decode_inbox_o", 2 * rows * world * D * 4)
     inbox_l = symm_ring.buffer("decode_inbox_lse", 2 * rows * world * 4)
     o_tab, l_tab = symm_ring.peer_ptr_table("decode_inbox_o"), symm_ring.peer_ptr_table("decode_inbox_lse")

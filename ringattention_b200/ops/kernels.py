@@ -223,12 +223,59 @@ def small_m_linear(x, w, out=None, residual=None):
     return out
 
 
+def _fused_small_m_ok(x, w, residual=None) -> bool:
+    """The prologue variant keeps f(x) (rows x K bf16) in shared memory."""
+    return (x.shape[0] <= 8 and x.is_contiguous() and w.is_contiguous() and x.dtype == torch.bfloat16
+            and (residual is None or residual.is_contiguous())
+            and x.shape[0] * w.shape[1] * 2 <= _lib.lib().ra_small_m_linear_fused_max_smem())
+
+
+def _small_m_linear_fused(x, w, residual, gain, eps, prologue):
+    M = x.shape[0]
+    N, Kd = w.shape
+    out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    _lib.call("ra_small_m_linear_fused", ptr(x), ptr(w), ptr(out), ptr(residual), ptr(gain), c_f(eps), prologue,
+              M, N, Kd, stream_ptr())
+    return out
+
+
 def linear_auto(x, w, out=None, residual=None):
     """Pick the tcgen05 GEMM or the small-M kernel by the number of rows."""
     if x.shape[0] <= 8 and x.is_contiguous() and (out is None or out.is_contiguous()) and \
             (residual is None or residual.is_contiguous()):
         return small_m_linear(x, w, out=out, residual=residual)
     return linear_fwd(x, w, out=out, residual=residual)
+
+
+def norm_linear(x, gain, eps: float, w):
+    """``rmsnorm(x) W^T``. For a handful of rows (decode) the normalisation runs in the prologue of the
+    weight-streaming kernel: one launch; otherwise the RMSNorm kernel and the GEMM."""
+    assert x.shape[1] == w.shape[1]
+    if _fused_small_m_ok(x, w):
+        return _small_m_linear_fused(x, w, None, gain, eps, 1)
+    h, _ = rmsnorm_fwd(x, gain, eps)
+    return linear_auto(h, w)
+
+
+def swiglu_linear(gu, w, residual=None):
+    """``(silu(gate) * up) W^T (+ residual)`` from the fused gate/up projection ``gu (M, 2F)``; one launch for
+    a handful of rows."""
+    assert gu.shape[1] == 2 * w.shape[1]
+    if _fused_small_m_ok(gu, w, residual):
+        return _small_m_linear_fused(gu, w, residual, None, 0.0, 2)
+    return linear_auto(swiglu_fwd(gu), w, residual=residual)
+
+
+def rope_append(qkv, k_cache, v_cache, pos_state, theta: float, k0: int = 0, stripe=None):
+    """RoPE of the q and k heads of a one-token ``(B, 1, 3, H, D)`` qkv buffer, in place, at the position in
+    ``pos_state[0]``, and the cache append of :func:`kv_append` (rotated K, V), in one launch."""
+    B, S_max, H, D = k_cache.shape
+    assert qkv.is_contiguous() and qkv.numel() == B * 3 * H * D
+    assert k_cache.stride() == v_cache.stride() and k_cache.stride(3) == 1
+    sn, sr, sb, sl = stripe if stripe is not None else (0, 0, 0, 0)
+    _lib.call("ra_rope_append", ptr(qkv), ptr(k_cache), ptr(v_cache), c_ll(k_cache.stride(0)),
+              c_ll(k_cache.stride(1)), c_ll(k_cache.stride(2)), ptr(pos_state), c_f(theta), c_ll(k0), S_max, B, H, D,
+              int(sn), int(sr), c_ll(sb), c_ll(sl), stream_ptr())
 
 
 def rope_at_(x, pos_state, theta: float, offset: int = 0):

@@ -132,6 +132,14 @@ class SymmRing:
             self._local[name] = t
         return t
 
+    def scratch_zeros(self, name: str, nbytes: int) -> torch.Tensor:
+        """Local device words that start at zero and keep their contents between calls (launch counters)."""
+        t = self._local.get(name)
+        if t is None:
+            t = torch.zeros((nbytes + 255) // 256 * 256, dtype=torch.uint8, device=self.device)
+            self._local[name] = t
+        return t
+
     def barrier(self) -> None:
         """Stream-ordered flag barrier across the ring; a missing peer ends in a status code."""
         _lib.call("ra_symm_barrier", c_vp(self._flag_ptrs.data_ptr()), self.rank, self.size,

@@ -142,6 +142,19 @@ def decode_engine(rank, world, dev):
         tok = lb.argmax(dim=-1)
     ok &= worst < 0.03
     print(f"[{rank}] decode logits, 6 teacher-forced steps: worst rel {worst:.4f}", flush=True)
+    # the same steps replayed from a CUDA graph (every exchange of the step inside the graph): the graph must give
+    # the logits of the eager step from the same state, which the single-device engine provides
+    agree = 0
+    for _ in range(4):
+        inf._tok_buf.copy_(tok.to(torch.int32).reshape(-1))
+        lb = single.decode_step(tok)
+        ta = inf.decode_step_graph().clone()
+        top2 = lb.topk(2).values[0]
+        # the graph's greedy token is the single-device argmax unless the two best logits are within bf16 noise
+        agree += int(ta[0]) == int(lb.argmax(dim=-1)[0]) or float(top2[0] - top2[1]) < 0.05 * float(lb.abs().max())
+        tok = lb.argmax(dim=-1)
+    ok &= agree == 4
+    print(f"[{rank}] graph-replayed sharded decode: {agree}/4 greedy tokens agree with one device", flush=True)
     # three streams on one shared context (striped over the ring), private tails dealt round-robin to the ranks
     sh = LlamaInference(cfg, max_context=8 * chunk, batch=1, seed=5, axis="sp", streams=3, max_new_tokens=16)
     sh1 = LlamaInference(cfg, max_context=8 * chunk, batch=1, seed=5, axis=None, streams=3, max_new_tokens=16)

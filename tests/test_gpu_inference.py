@@ -54,6 +54,93 @@ def test_small_m_linear():
         assert (y.float() - ref).abs().max() <= 0.01 * ref.abs().max() + 0.05
 
 
+def test_small_m_linear_prologues():
+    """RMSNorm and SwiGLU applied while the kernel reads x, against plain fp32 PyTorch."""
+    from ringattention_b200.ops import kernels as K
+
+    torch.manual_seed(2)
+    for M in (1, 4, 8):
+        x = torch.randn(M, 1024, device="cuda").bfloat16()
+        g = (1 + 0.1 * torch.randn(1024, device="cuda")).bfloat16()
+        w = (torch.randn(776, 1024, device="cuda") / 32).bfloat16()
+        y = K.norm_linear(x, g, 1e-5, w)
+        xf = x.float()
+        ref = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()) @ w.float().t()
+        assert (y.float() - ref).abs().max() <= 0.01 * ref.abs().max() + 0.02
+
+        gu = torch.randn(M, 2 * 1024, device="cuda").bfloat16()
+        r = torch.randn(M, 776, device="cuda").bfloat16()
+        y = K.swiglu_linear(gu, w, residual=r)
+        h = (torch.nn.functional.silu(gu[:, :1024].float()) * gu[:, 1024:].float()).bfloat16().float()
+        ref = h @ w.float().t() + r.float()
+        assert (y.float() - ref).abs().max() <= 0.01 * ref.abs().max() + 0.02
+        # the same numbers as the two-launch path: the activation is rounded to bf16 in both
+        two = K.small_m_linear(K.swiglu_fwd(gu), w, residual=r)
+        assert torch.equal(y, two)
+
+
+@pytest.mark.parametrize("D,striped", [(128, False), (64, True)])
+def test_rope_append_equals_rope_then_append(D, striped):
+    from ringattention_b200.ops import kernels as K
+
+    torch.manual_seed(3)
+    B, H, S_max = 2, 8, 64
+    qkv = torch.randn(B, 1, 3, H, D, device="cuda").bfloat16()
+    state = torch.tensor([37, 0], device="cuda", dtype=torch.int64)
+    stripe = (2, 1, 16, 32) if striped else None  # decoded token 5 -> rank 1, row 16 + 2
+    caches = [torch.zeros(B, 2, H, S_max, D, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    views = [(c[:, 0].transpose(1, 2), c[:, 1].transpose(1, 2)) for c in caches]
+    a = qkv.clone()
+    K.rope_at_(a.view(B, 1, 3 * H, D)[:, :, :2 * H], state, 10000.0)
+    K.kv_append(a, views[0][0], views[0][1], state, stripe=stripe)
+    b = qkv.clone()
+    K.rope_append(b, views[1][0], views[1][1], state, 10000.0, stripe=stripe)
+    assert torch.equal(a, b) and torch.equal(caches[0], caches[1])
+    row = 18 if striped else 37
+    assert torch.equal(views[1][0][:, row], b[:, 0, 1]) and torch.equal(views[1][1][:, row], b[:, 0, 2])
+    written = int(torch.count_nonzero(views[1][0][:, row])) + int(torch.count_nonzero(views[1][1][:, row]))
+    assert int(torch.count_nonzero(caches[1])) == written  # no other cache row was touched
+
+
+def test_merge_exchange_gives_up_on_a_silent_peer_and_still_merges_its_own_rows():
+    """The one-launch cross-GPU merge with a second "rank" that never signals (its buffers are local and nobody
+    writes them): every row's wait runs out, the status word gets the peer-timeout code, the kernel returns and
+    the context keeps working. The silent rank's inbox slots hold lse = -inf, so the merged rows equal this
+    rank's own."""
+    import ctypes
+
+    from ringattention_b200.ops import _lib
+    from ringattention_b200.ops import decode as Dk
+
+    torch.manual_seed(4)
+    rows, parts, D, n = 16, 3, 128, 2
+    o_part = torch.randn(rows, parts, D, device="cuda")
+    lse_part = torch.randn(rows, parts, device="cuda")
+    boxes_o = torch.zeros(n, 2, rows, n, D, device="cuda")
+    boxes_l = torch.full((n, 2, rows, n), float("-inf"), device="cuda")
+    flags = torch.zeros(n, rows, n, dtype=torch.int32, device="cuda")
+    sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+    tab = lambda t: torch.tensor([t[i].data_ptr() for i in range(n)], dtype=torch.int64, device="cuda")
+    to, tl, tf = tab(boxes_o), tab(boxes_l), tab(flags)
+    out = torch.empty(rows, D, device="cuda")
+    st = _lib.status_tensor()
+    st.zero_()
+    vp = ctypes.c_void_p
+    _lib.call("ra_decode_merge_exchange", vp(o_part.data_ptr()), vp(lse_part.data_ptr()),
+              ctypes.c_longlong(parts * D), ctypes.c_longlong(D), ctypes.c_longlong(parts), ctypes.c_longlong(1),
+              rows, parts, D, 1, 0, vp(out.data_ptr()), 1, vp(to.data_ptr()), vp(tl.data_ptr()),
+              vp(boxes_o[0].data_ptr()), vp(boxes_l[0].data_ptr()), rows, vp(tf.data_ptr()), vp(sync.data_ptr()), n, 0,
+              ctypes.c_ulonglong(50_000_000), vp(st.data_ptr()), _lib.stream_ptr())
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.KernelError, match="peer flag"):
+        _lib.check_status()
+    assert sync.tolist() == [1, 0]  # the launch counter advanced, the arrival counter is back at zero
+    w = torch.softmax(lse_part, dim=1)
+    ref = (w[:, :, None] * o_part).sum(1)
+    assert (out - ref).abs().max() < 1e-4
+    assert Dk.exchange_fits(rows) and not Dk.exchange_fits(10 ** 6)
+
+
 def test_prefill_and_greedy_decode_match_full_forward():
     from ringattention_b200.config import LlamaConfig
     from ringattention_b200.models.llama_infer import LlamaInference
