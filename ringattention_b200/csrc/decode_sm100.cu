@@ -75,12 +75,31 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return u;
 }
 
-// D = head dim (64 or 128), QL = query rows held per CTA.
-template <int D, int QL>
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros without reading the source.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int DEC_UNROLL = 4;  // cache rows per thread and loop trip
+
+// D = head dim (64 or 128), QL = query rows held per CTA, ST = stages of the asynchronous-copy ring (0: the rows
+// of a trip are loaded straight into registers). With ST > 0 every thread copies the rows of trip i + ST - 1 into
+// its own shared-memory slots (cp.async, no registers held while the data is in flight) before it works on trip
+// i, so memory requests are outstanding during the arithmetic too; a thread only ever reads what it copied itself,
+// hence cp.async.wait_group is all the synchronisation needed. Dynamic shared memory: ST * 4 rows * 32 bytes per
+// thread.
+template <int D, int QL, int ST>
 __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitParams p) {
   constexpr int LPR = D / 8;        // lanes per cache row (16 bytes per lane)
   constexpr int RPW = 32 / LPR;     // rows per warp step
-  constexpr int UNROLL = 4;  // cache rows in flight per thread (8 made it slower: 4.6 vs 5.2 TB/s, fewer CTAs per SM)
+  constexpr int UNROLL = DEC_UNROLL;  // cache rows in flight per thread (8 made it slower: 4.6 vs 5.2 TB/s, fewer CTAs per SM)
+  extern __shared__ uint4 stage_buf[];  // [ST][UNROLL][k|v][THREADS]
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPR, dl = lane % LPR;  // which row of the step, which 8-wide slice of D
@@ -124,20 +143,58 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
 
   // The trip count is the same for every lane of a warp (the loop variable ignores `sub`), so the
   // full-mask shuffles below always see all 32 lanes; rows past the end are merely masked out.
+  // stage `slot` <- the rows of the trip that starts at row base_w (of this warp)
+  auto issue = [&](int base_w, int slot) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int r = base_w + sub + u * step;
+      const bool in = r < r1;
+      const long long rr = in ? r : r0;  // r0 < r1 whenever the loop runs: a valid address, never read when !in
+      uint4* dst = stage_buf + ((slot * UNROLL + u) * 2) * THREADS + threadIdx.x;
+      cp_async16(dst, kb + rr * p.k_ss, in ? 16 : 0);
+      cp_async16(dst + THREADS, vb + rr * p.v_ss, in ? 16 : 0);
+    }
+  };
+  int ahead_w = r0 + warp * RPW, slot_in = 0, slot_out = 0;
+  if (ST > 0) {
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+      if (ahead_w < r1) issue(ahead_w, slot_in);
+      cp_async_commit();  // one group per trip, empty or not, so that the group count below is a constant
+      ahead_w += step * UNROLL;
+      slot_in = slot_in + 1 == ST ? 0 : slot_in + 1;
+    }
+  }
   for (int base_w = r0 + warp * RPW; base_w < r1; base_w += step * UNROLL) {
     const int base = base_w + sub;
     uint4 ku[UNROLL], vu[UNROLL];
     bool ok[UNROLL];
+    if (ST > 0) {
+      if (ahead_w < r1) issue(ahead_w, slot_in);
+      cp_async_commit();
+      ahead_w += step * UNROLL;
+      slot_in = slot_in + 1 == ST ? 0 : slot_in + 1;
+      cp_async_wait<(ST > 0 ? ST - 1 : 0)>();  // all but the newest ST - 1 groups are complete: this trip's rows are in
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int r = base + u * step;
-      ok[u] = r < r1;
-      if (ok[u]) {
-        ku[u] = *reinterpret_cast<const uint4*>(kb + static_cast<long long>(r) * p.k_ss);
-        vu[u] = *reinterpret_cast<const uint4*>(vb + static_cast<long long>(r) * p.v_ss);
-      } else {
-        ku[u] = make_uint4(0, 0, 0, 0);
-        vu[u] = make_uint4(0, 0, 0, 0);
+      for (int u = 0; u < UNROLL; ++u) {
+        ok[u] = base + u * step < r1;
+        const uint4* src = stage_buf + ((slot_out * UNROLL + u) * 2) * THREADS + threadIdx.x;
+        ku[u] = src[0];
+        vu[u] = src[THREADS];
+      }
+      slot_out = slot_out + 1 == ST ? 0 : slot_out + 1;
+    } else {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int r = base + u * step;
+        ok[u] = r < r1;
+        if (ok[u]) {
+          ku[u] = *reinterpret_cast<const uint4*>(kb + static_cast<long long>(r) * p.k_ss);
+          vu[u] = *reinterpret_cast<const uint4*>(vb + static_cast<long long>(r) * p.v_ss);
+        } else {
+          ku[u] = make_uint4(0, 0, 0, 0);
+          vu[u] = make_uint4(0, 0, 0, 0);
+        }
       }
     }
     float s[UNROLL][QL];
@@ -183,6 +240,7 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
     }
   }
 
+  if (ST > 0) cp_async_wait<0>();  // only empty groups can be left; nothing is in flight when the CTA ends
   // ---- combine the row groups of a warp, then the warps of the CTA
   __shared__ float sm_m[WARPS][QL], sm_l[WARPS][QL];
   __shared__ float sm_o[WARPS][QL][D];
@@ -498,7 +556,7 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16
 // against it; the launcher picks cpw so that the whole grid is resident at once. Each warp issues the first
 // weight loads of its first column before the prologue, so the prologue's latency hides behind them. (Applying
 // f inside every warp's k loop instead repeats it N times and made a 7B decode step 9 % slower.)
-enum { PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
+enum { PRO_COPY = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };  // PRO_COPY: f(x) = x, staged in shared memory like the others
 
 template <int M, int PRO>
 __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bfloat16* __restrict__ x,
@@ -529,6 +587,10 @@ __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bflo
     const long long ldx = PRO == PRO_SWIGLU ? 2ll * K : K;
     const uint4* xr = reinterpret_cast<const uint4*>(x + m * ldx);
     for (int c = tid; c < n16; c += 256) {
+      if (PRO == PRO_COPY) {
+        xs[m * n16 + c] = xr[c];
+        continue;
+      }
       float xf[8], of[8];
       unpack8(xr[c], xf);
       unpack8(PRO == PRO_SWIGLU ? xr[c + n16] : reinterpret_cast<const uint4*>(gain)[c], of);
@@ -697,6 +759,7 @@ struct RaDecodeArgs {
   int stripe_n, stripe_rank;
   long long stripe_base, stripe_len0;
   void* stream;
+  int stages;  // 0, 3 or 4: depth of the asynchronous-copy ring of the cache rows
 };
 
 extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
@@ -728,12 +791,33 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
   p.stripe_base = a->stripe_base; p.stripe_len0 = a->stripe_len0;
   dim3 grid(a->splits, a->H, a->B);
   cudaStream_t s = static_cast<cudaStream_t>(a->stream);
-#define RA_LAUNCH_DEC(DD, QQ) decode_splitkv_kernel<DD, QQ><<<grid, THREADS, 0, s>>>(p)
   const int ql = a->QL <= 1 ? 1 : (a->QL <= 2 ? 2 : (a->QL <= 4 ? 4 : 8));
   if (ql != a->QL) {
     set_error("ra_decode_splitkv: q_len must be 1, 2, 4 or 8 (pad the query)");
     return kHostBadArg;
   }
+  if (a->stages != 0 && a->stages != 3 && a->stages != 4) {
+    set_error("ra_decode_splitkv: stages must be 0, 3 or 4");
+    return kHostBadArg;
+  }
+#define RA_LAUNCH_DEC3(DD, QQ, SS)                                                                          \
+  do {                                                                                                      \
+    constexpr int smem = SS * DEC_UNROLL * 2 * THREADS * 16;                                                \
+    static bool attr_done[64] = {};                                                                         \
+    int dev = 0;                                                                                            \
+    cudaGetDevice(&dev);                                                                                    \
+    if (smem > 48 * 1024 && dev < 64 && !attr_done[dev]) {                                                  \
+      cudaFuncSetAttribute(decode_splitkv_kernel<DD, QQ, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      attr_done[dev] = true;                                                                                \
+    }                                                                                                       \
+    decode_splitkv_kernel<DD, QQ, SS><<<grid, THREADS, smem, s>>>(p);                                       \
+  } while (0)
+#define RA_LAUNCH_DEC(DD, QQ)                                                                               \
+  do {                                                                                                      \
+    if (a->stages == 3) RA_LAUNCH_DEC3(DD, QQ, 3);                                                          \
+    else if (a->stages == 4) RA_LAUNCH_DEC3(DD, QQ, 4);                                                     \
+    else RA_LAUNCH_DEC3(DD, QQ, 0);                                                                         \
+  } while (0)
   if (a->D == 128) {
     if (ql == 1) RA_LAUNCH_DEC(128, 1); else if (ql == 2) RA_LAUNCH_DEC(128, 2);
     else if (ql == 4) RA_LAUNCH_DEC(128, 4); else RA_LAUNCH_DEC(128, 8);
@@ -742,6 +826,7 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
     else if (ql == 4) RA_LAUNCH_DEC(64, 4); else RA_LAUNCH_DEC(64, 8);
   }
 #undef RA_LAUNCH_DEC
+#undef RA_LAUNCH_DEC3
   return check_launch("decode_splitkv_kernel");
 }
 
@@ -867,10 +952,10 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
                                        float eps, int prologue, int M, int N, int K, void* stream) {
   using namespace ra::decode;
   const long long smem = static_cast<long long>(M) * K * 2;
-  if (M < 1 || M > 8 || K % 8 || N < 1 || (prologue != PRO_RMSNORM && prologue != PRO_SWIGLU) ||
+  if (M < 1 || M > 8 || K % 8 || N < 1 || prologue < PRO_COPY || prologue > PRO_SWIGLU ||
       (prologue == PRO_RMSNORM && !gain) || smem > ra_small_m_linear_fused_max_smem()) {
-    set_error("ra_small_m_linear_fused: need 1 <= M <= 8, K % 8 == 0, M * K * 2 <= 48 KB, a prologue of 1 (RMSNorm, "
-              "with a gain) or 2 (SwiGLU)");
+    set_error("ra_small_m_linear_fused: need 1 <= M <= 8, K % 8 == 0, M * K * 2 <= 48 KB, a prologue of 0 (none), "
+              "1 (RMSNorm, with a gain) or 2 (SwiGLU)");
     return kHostBadArg;
   }
   // columns per warp: the whole grid resident at once (four CTAs of 256 threads per SM)
@@ -886,7 +971,9 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
   const __nv_bfloat16* gg = static_cast<const __nv_bfloat16*>(gain);
 #define RA_SML_CASE(MM)                                                                                        \
   case MM:                                                                                                     \
-    if (prologue == PRO_RMSNORM)                                                                               \
+    if (prologue == PRO_COPY)                                                                                  \
+      small_m_linear_pro_kernel<MM, PRO_COPY><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw);    \
+    else if (prologue == PRO_RMSNORM)                                                                          \
       small_m_linear_pro_kernel<MM, PRO_RMSNORM><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw); \
     else                                                                                                       \
       small_m_linear_pro_kernel<MM, PRO_SWIGLU><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw);  \

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -16,6 +17,10 @@ from . import _lib
 
 c_ll = ctypes.c_longlong
 c_vp = ctypes.c_void_p
+
+
+# Depth of the split-KV kernel's asynchronous-copy ring for the cache rows (0: plain loads into registers).
+STAGES = int(os.environ.get("RINGATTN_B200_DECODE_STAGES", "0"))
 
 
 class _DecodeArgs(ctypes.Structure):
@@ -32,6 +37,7 @@ class _DecodeArgs(ctypes.Structure):
         ("stripe_n", ctypes.c_int), ("stripe_rank", ctypes.c_int),
         ("stripe_base", c_ll), ("stripe_len0", c_ll),
         ("stream", c_vp),
+        ("stages", ctypes.c_int),
     ]
 
 
@@ -84,6 +90,7 @@ def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, 
     # striped cache (with pos_ptr): (ranks, rank, prefilled rows per rank, prefilled positions)
     a.stripe_n, a.stripe_rank, a.stripe_base, a.stripe_len0 = stripe if stripe is not None else (0, 0, 0, 0)
     a.stream = torch.cuda.current_stream().cuda_stream
+    a.stages = STAGES
     _lib.call("ra_decode_splitkv", ctypes.byref(a))
     return o_part, lse_part
 

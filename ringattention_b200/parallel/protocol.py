@@ -173,3 +173,43 @@ def check_schedule(programs: List[List[Op]]) -> Optional[str]:
                 seen.add(t)
                 stack.append(t)
     return None
+
+
+def check_row_exchange(n: int, rows: int, launches: int, slots: int = 2) -> Optional[str]:
+    """The one-launch decode exchange (``decode_merge_exchange_kernel``): in launch ``e`` CTA ``row`` of every rank
+    stores its partial into slot ``e % slots`` of every rank's inbox and raises the row's flag there, waits for the
+    row's flag of launch ``e`` from every rank and merges the row of its own inbox; a rank starts launch ``e + 1``
+    when all its rows are done. There is no barrier: ranks only meet row by row. Explores every interleaving of
+    these steps and returns a description of the first store that lands in an inbox slot whose previous content has
+    not been merged yet, or ``None``."""
+    # per rank: (launch, phases) with phase 0 = nothing yet, 1 = stored and flagged (waiting), 2 = merged
+    start = tuple((0, (0,) * rows) for _ in range(n))
+    seen, stack = {start}, [start]
+    while stack:
+        st = stack.pop()
+        for r in range(n):
+            e, ph = st[r]
+            if e >= launches:
+                continue
+            for row in range(rows):
+                if ph[row] == 0:  # store + flag
+                    for t in range(n):
+                        te, tph = st[t]
+                        merged = te + (1 if te < launches and tph[row] == 2 else 0)  # launches whose row t has merged
+                        if merged < e - slots + 1:
+                            return (f"rank {r} launch {e} row {row} overwrites slot {e % slots} of rank {t}, "
+                                    f"which has merged only {merged} launches")
+                    nph = ph[:row] + (1,) + ph[row + 1:]
+                elif ph[row] == 1:  # wait for the row of every rank, then merge
+                    if not all(se > e or (se == e and sph[row] >= 1) for se, sph in st):
+                        continue
+                    nph = ph[:row] + (2,) + ph[row + 1:]
+                else:
+                    continue
+                nst = list(st)
+                nst[r] = (e + 1, (0,) * rows) if all(x == 2 for x in nph) else (e, nph)
+                t = tuple(nst)
+                if t not in seen:
+                    seen.add(t)
+                    stack.append(t)
+    return None

@@ -129,6 +129,10 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--decode-stages", type=int, default=None, choices=[0, 3, 4],
+                    help="decode: depth of the asynchronous-copy ring of the cache rows (default: the library's)")
+    ap.add_argument("--prologue", default="none", choices=["none", "staged", "rmsnorm", "swiglu"],
+                    help="small_m_linear: apply RMSNorm or SwiGLU to the input inside the kernel")
     ap.add_argument("--cache-layout", default="heads", choices=["rows", "heads"],
                     help="decode: (B, S, 2, H, D) rows-major cache or (B, 2, H, S, D) heads-major cache")
     ap.add_argument("--mean-doc-len", type=int, default=0,
@@ -208,8 +212,11 @@ def main(argv=None) -> int:
         else:  # every (kv, head) is one contiguous stream of S rows
             cache = torch.randn(B, 2, H, S, D, device=dev).bfloat16()
             ck, cv = cache[:, 0].permute(0, 2, 1, 3), cache[:, 1].permute(0, 2, 1, 3)
+        if args.decode_stages is not None:
+            Dk.STAGES = args.decode_stages
         fn = lambda: Dk.decode_partial(q, ck, cv, q_pos0=S, k_pos0=0)
         res["cache_layout"] = args.cache_layout
+        res["stages"] = Dk.STAGES
         flops = 4.0 * B * S * H * D
         bytes_ = 2.0 * B * S * H * D * 2
         res.update(shape=[B, S, H, D], splits=Dk.default_splits(S, B, H))
@@ -220,9 +227,20 @@ def main(argv=None) -> int:
         x = torch.randn(M, Kd, device=dev).bfloat16()
         turn = [0]
 
+        gain = torch.ones(Kd, device=dev).bfloat16()
+        gu = torch.randn(M, 2 * Kd, device=dev).bfloat16()
+
         def fn():
             turn[0] = (turn[0] + 1) % len(ws)
-            K.small_m_linear(x, ws[turn[0]])
+            if args.prologue == "rmsnorm":  # RMSNorm(x) W^T in one launch
+                K.norm_linear(x, gain, 1e-5, ws[turn[0]])
+            elif args.prologue == "swiglu":  # (silu(gate) * up) W^T in one launch
+                K.swiglu_linear(gu, ws[turn[0]])
+            else:
+                K.small_m_linear(x, ws[turn[0]])
+
+        K.SMALL_M_STAGED = args.prologue == "staged"
+        res["prologue"] = args.prologue
 
         flops = 2.0 * M * N * Kd
         bytes_ = 2.0 * N * Kd

@@ -57,3 +57,12 @@ def test_fsdp_needs_the_collectives_around_the_update():
     assert check_schedule([fsdp_program(r, 2, steps=2, sync_after_update=False) for r in range(2)]) is not None
     # without the gradient collective a rank may rewrite its shard while a slower peer still reads it
     assert check_schedule([fsdp_program(r, 2, steps=1, reduce_before_update=False) for r in range(2)]) is not None
+
+
+@pytest.mark.parametrize("n,rows", [(2, 2), (3, 2), (2, 3)])
+def test_row_exchange_with_two_slots_is_race_free(n, rows):
+    assert P.check_row_exchange(n, rows, launches=4) is None
+
+
+def test_row_exchange_with_one_slot_overwrites_unmerged_rows():
+    assert "overwrites" in (P.check_row_exchange(2, 2, launches=2, slots=1) or "")
