@@ -37,6 +37,8 @@ NVCC_FLAGS = [
 # RINGATTN_B200_BOUNDS_CHECK=1 builds the checked variant of the library (libringattn_b200_chk.so): the kernels
 # range-check their global-memory indices and record a violation in the status word instead of making the access
 BOUNDS_CHECK = os.environ.get("RINGATTN_B200_BOUNDS_CHECK") == "1"
+# extra compiler flags (e.g. a -D to try a tuning constant); they are part of the objects' digest
+NVCC_FLAGS += os.environ.get("RINGATTN_B200_NVCC_FLAGS", "").split()
 if BOUNDS_CHECK:
     NVCC_FLAGS.append("-DRA_BOUNDS_CHECK=1")
     OBJ_DIR = OUT_DIR / "obj_chk"

@@ -759,7 +759,7 @@ struct RaDecodeArgs {
   int stripe_n, stripe_rank;
   long long stripe_base, stripe_len0;
   void* stream;
-  int stages;  // 0, 3 or 4: depth of the asynchronous-copy ring of the cache rows
+  int stages;  // 0, 3 or 4: depth of the asynchronous-copy ring of the cache rows (0: loads into registers)
 };
 
 extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
@@ -800,13 +800,14 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
     set_error("ra_decode_splitkv: stages must be 0, 3 or 4");
     return kHostBadArg;
   }
+// (the dynamic ring plus the static arrays exceed 48 KB for every ST > 0, hence the attribute)
 #define RA_LAUNCH_DEC3(DD, QQ, SS)                                                                          \
   do {                                                                                                      \
     constexpr int smem = SS * DEC_UNROLL * 2 * THREADS * 16;                                                \
     static bool attr_done[64] = {};                                                                         \
     int dev = 0;                                                                                            \
     cudaGetDevice(&dev);                                                                                    \
-    if (smem > 48 * 1024 && dev < 64 && !attr_done[dev]) {                                                  \
+    if (smem > 0 && dev < 64 && !attr_done[dev]) {                                                          \
       cudaFuncSetAttribute(decode_splitkv_kernel<DD, QQ, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       attr_done[dev] = true;                                                                                \
     }                                                                                                       \
