@@ -239,10 +239,12 @@ def _fused_small_m_ok(x, w, residual=None) -> bool:
             and x.shape[0] * w.shape[1] * 2 <= _lib.lib().ra_small_m_linear_fused_max_smem())
 
 
-def _small_m_linear_fused(x, w, residual, gain, eps, prologue):
+def _small_m_linear_fused(x, w, residual, gain, eps, prologue, out=None):
     M = x.shape[0]
     N, Kd = w.shape
-    out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    assert out.is_contiguous() and out.shape == (M, N)
     _lib.call("ra_small_m_linear_fused", ptr(x), ptr(w), ptr(out), ptr(residual), ptr(gain), c_f(eps), prologue,
               M, N, Kd, stream_ptr())
     return out
@@ -256,23 +258,23 @@ def linear_auto(x, w, out=None, residual=None):
     return linear_fwd(x, w, out=out, residual=residual)
 
 
-def norm_linear(x, gain, eps: float, w):
+def norm_linear(x, gain, eps: float, w, out=None):
     """``rmsnorm(x) W^T``. For a handful of rows (decode) the normalisation runs in the prologue of the
     weight-streaming kernel: one launch; otherwise the RMSNorm kernel and the GEMM."""
     assert x.shape[1] == w.shape[1]
     if _fused_small_m_ok(x, w):
-        return _small_m_linear_fused(x, w, None, gain, eps, 1)
+        return _small_m_linear_fused(x, w, None, gain, eps, 1, out=out)
     h, _ = rmsnorm_fwd(x, gain, eps)
-    return linear_auto(h, w)
+    return linear_auto(h, w, out=out)
 
 
-def swiglu_linear(gu, w, residual=None):
+def swiglu_linear(gu, w, residual=None, out=None):
     """``(silu(gate) * up) W^T (+ residual)`` from the fused gate/up projection ``gu (M, 2F)``; one launch for
     a handful of rows."""
     assert gu.shape[1] == 2 * w.shape[1]
     if _fused_small_m_ok(gu, w, residual):
-        return _small_m_linear_fused(gu, w, residual, None, 0.0, 2)
-    return linear_auto(swiglu_fwd(gu), w, residual=residual)
+        return _small_m_linear_fused(gu, w, residual, None, 0.0, 2, out=out)
+    return linear_auto(swiglu_fwd(gu), w, out=out, residual=residual)
 
 
 def rope_append(qkv, k_cache, v_cache, pos_state, theta: float, k0: int = 0, stripe=None):

@@ -89,6 +89,23 @@ def main():
     K.adamw_(p32, m, vv, gr, canary((n,), bf), step=1, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
              decay_end=4000)
     K.cast_f32_to_bf16(torch.randn(19, 72, device=dev), canary((19, 72), bf))
+    # ---- decode family: split-KV attention over a heads-major cache, merge, weight-streaming linears with their
+    # prologues, RoPE + cache append
+    from ringattention_b200.ops import decode as Dk
+
+    B, H, D, S = 2, 3, 128, 777
+    cache = canary((B, 2, H, S, D), bf, fill=torch.randn(B, 2, H, S, D, device=dev).to(bf))
+    ck, cv = cache[:, 0].permute(0, 2, 1, 3), cache[:, 1].permute(0, 2, 1, 3)
+    qd = torch.randn(B, 1, H, D, device=dev).to(bf)
+    o_part, lse_part = Dk.decode_partial(qd, ck, cv, q_pos0=S, k_pos0=0)
+    Dk.merge_partials(o_part, lse_part, H, 1, out=canary((B, 1, H, D), bf))
+    xs_, ws_ = torch.randn(3, 520, device=dev).to(bf), (torch.randn(203, 520, device=dev) * 0.05).to(bf)
+    K.small_m_linear(xs_, ws_, out=canary((3, 203), bf))
+    K.norm_linear(xs_, torch.ones(520, device=dev).to(bf), 1e-6, ws_, out=canary((3, 203), bf))
+    K.swiglu_linear(torch.randn(3, 1040, device=dev).to(bf), ws_, out=canary((3, 203), bf))
+    qkv = canary((B, 1, 3, H, D), bf, fill=torch.randn(B, 1, 3, H, D, device=dev).to(bf))
+    K.rope_append(qkv, ck, cv, torch.tensor([S - 1, 0], device=dev, dtype=torch.int64), 10000.0)
+    K.rope_append(qkv, ck, cv, torch.tensor([S + 5, 0], device=dev, dtype=torch.int64), 10000.0)  # not on this shard
     torch.cuda.synchronize()
     _lib.check_status()
     clean = _lib.bounds_report(reset=True)
