@@ -241,7 +241,7 @@ class LlamaInference:
     @torch.no_grad()
     def decode_step_graph(self) -> torch.Tensor:
         """Greedy step on the token in ``self._tok_buf`` through a CUDA graph recorded on first use:
-        one replay per token instead of ~15 launches per layer. Writes the next token back into
+        one replay per token instead of 7 launches per layer. Writes the next token back into
         ``self._tok_buf`` and returns it. Call :meth:`decode_step` at least once before (buffers and
         kernels must exist before capture)."""
         if self._graph is None:
