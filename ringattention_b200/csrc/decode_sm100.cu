@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const __nv_bfloat16
 // against it; the launcher picks cpw so that the whole grid is resident at once. Each warp issues the first
 // weight loads of its first column before the prologue, so the prologue's latency hides behind them. (Applying
 // f inside every warp's k loop instead repeats it N times and made a 7B decode step 9 % slower.)
-enum { PRO_COPY = 0, PRO_RMSNORM = 1, PRO_SWIGLU = 2 };  // PRO_COPY: f(x) = x, staged in shared memory like the others
+enum { PRO_RMSNORM = 1, PRO_SWIGLU = 2 };
 
 template <int M, int PRO>
 __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bfloat16* __restrict__ x,
@@ -587,10 +587,6 @@ __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bflo
     const long long ldx = PRO == PRO_SWIGLU ? 2ll * K : K;
     const uint4* xr = reinterpret_cast<const uint4*>(x + m * ldx);
     for (int c = tid; c < n16; c += 256) {
-      if (PRO == PRO_COPY) {
-        xs[m * n16 + c] = xr[c];
-        continue;
-      }
       float xf[8], of[8];
       unpack8(xr[c], xf);
       unpack8(PRO == PRO_SWIGLU ? xr[c + n16] : reinterpret_cast<const uint4*>(gain)[c], of);
@@ -953,10 +949,10 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
                                        float eps, int prologue, int M, int N, int K, void* stream) {
   using namespace ra::decode;
   const long long smem = static_cast<long long>(M) * K * 2;
-  if (M < 1 || M > 8 || K % 8 || N < 1 || prologue < PRO_COPY || prologue > PRO_SWIGLU ||
+  if (M < 1 || M > 8 || K % 8 || N < 1 || (prologue != PRO_RMSNORM && prologue != PRO_SWIGLU) ||
       (prologue == PRO_RMSNORM && !gain) || smem > ra_small_m_linear_fused_max_smem()) {
-    set_error("ra_small_m_linear_fused: need 1 <= M <= 8, K % 8 == 0, M * K * 2 <= 48 KB, a prologue of 0 (none), "
-              "1 (RMSNorm, with a gain) or 2 (SwiGLU)");
+    set_error("ra_small_m_linear_fused: need 1 <= M <= 8, K % 8 == 0, M * K * 2 <= 48 KB, a prologue of 1 (RMSNorm, "
+              "with a gain) or 2 (SwiGLU)");
     return kHostBadArg;
   }
   // columns per warp: the whole grid resident at once (four CTAs of 256 threads per SM)
@@ -972,9 +968,7 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
   const __nv_bfloat16* gg = static_cast<const __nv_bfloat16*>(gain);
 #define RA_SML_CASE(MM)                                                                                        \
   case MM:                                                                                                     \
-    if (prologue == PRO_COPY)                                                                                  \
-      small_m_linear_pro_kernel<MM, PRO_COPY><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw);    \
-    else if (prologue == PRO_RMSNORM)                                                                          \
+    if (prologue == PRO_RMSNORM)                                                                               \
       small_m_linear_pro_kernel<MM, PRO_RMSNORM><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw); \
     else                                                                                                       \
       small_m_linear_pro_kernel<MM, PRO_SWIGLU><<<blocks, 256, smem, s>>>(xx, ww, yy, rr, gg, eps, N, K, cpw);  \

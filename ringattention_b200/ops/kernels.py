@@ -210,11 +210,6 @@ def cast_bf16_to_f32(src, dst):
     return dst
 
 
-# The plain product through the shared-memory variant too (x staged once per CTA, resident grid, weight loads of
-# the next group issued before the current one is consumed).
-SMALL_M_STAGED = False
-
-
 def small_m_linear(x, w, out=None, residual=None):
     """``y = x W^T (+ residual)`` for at most 8 rows: a bandwidth-bound kernel that reads every weight
     row once (decode steps). ``x (M,K)``, ``w (N,K)`` bf16 contiguous."""
@@ -224,10 +219,6 @@ def small_m_linear(x, w, out=None, residual=None):
     if out is None:
         out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
     assert out.is_contiguous() and (residual is None or residual.is_contiguous())
-    if SMALL_M_STAGED and _fused_small_m_ok(x, w, residual):
-        _lib.call("ra_small_m_linear_fused", ptr(x), ptr(w), ptr(out), ptr(residual), ptr(None), c_f(0.0), 0,
-                  M, N, Kd, stream_ptr())
-        return out
     _lib.call("ra_small_m_linear", ptr(x), ptr(w), ptr(out), ptr(residual), M, N, Kd, stream_ptr())
     return out
 

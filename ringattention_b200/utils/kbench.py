@@ -131,7 +131,7 @@ def main(argv=None) -> int:
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--decode-stages", type=int, default=None, choices=[0, 3, 4],
                     help="decode: depth of the asynchronous-copy ring of the cache rows (default: the library's)")
-    ap.add_argument("--prologue", default="none", choices=["none", "staged", "rmsnorm", "swiglu"],
+    ap.add_argument("--prologue", default="none", choices=["none", "rmsnorm", "swiglu"],
                     help="small_m_linear: apply RMSNorm or SwiGLU to the input inside the kernel")
     ap.add_argument("--cache-layout", default="heads", choices=["rows", "heads"],
                     help="decode: (B, S, 2, H, D) rows-major cache or (B, 2, H, S, D) heads-major cache")
@@ -239,7 +239,6 @@ def main(argv=None) -> int:
             else:
                 K.small_m_linear(x, ws[turn[0]])
 
-        K.SMALL_M_STAGED = args.prologue == "staged"
         res["prologue"] = args.prologue
 
         flops = 2.0 * M * N * Kd
