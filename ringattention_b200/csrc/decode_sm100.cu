@@ -290,6 +290,230 @@ __global__ void __launch_bounds__(THREADS) decode_splitkv_kernel(const SplitPara
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same split-KV pass on the tensor cores, for calls with several query rows per cache row (shared-prefix
+// streams, short speculative or multi-token steps). With q rows the CUDA-core kernel above spends q times the
+// instructions per cache row and becomes bound by its instruction stream (four rows: twice the time of one).
+// Here the <= 8 query rows are the M side of a 16 x 8 x 16 MMA (rows 8..15 are zero), the cache rows its N side:
+//   S (16 x 16 kv)  = Q (16 x D) K_chunk^T        2 n-tiles x D/16 k-steps, B fragments by ldmatrix
+//   O (16 x D)     += P (16 x 16 kv) V_chunk      D/8 n-tiles, B fragments by ldmatrix.trans, P from the S fragments
+// so a chunk of 16 cache rows costs 2 * D/8 MMAs and D/8 ldmatrix whatever the number of query rows. Every warp walks
+// its own chunks and stages them through its own three-stage cp.async ring in shared memory (16-byte pieces,
+// XOR-swizzled by the row so that ldmatrix is conflict-free); only __syncwarp() is needed around a stage. The legacy
+// mma.sync path is the right size here: the kernel is bound by HBM, a 128-row tcgen05 tile would bring nothing but a
+// longer hand-off chain per tile.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+// d += a * b for m16n8k16, bf16 inputs, fp32 accumulation; rows 8..15 of a are zero (a1 = a3 = 0)
+__device__ __forceinline__ void mma_16816_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+constexpr int MMA_ST = 3;       // stages of a warp's ring
+constexpr int MMA_ROWS = 16;    // cache rows per chunk
+
+template <int D>
+__global__ void __launch_bounds__(THREADS) decode_splitkv_mma_kernel(const SplitParams p, int QL) {
+  constexpr int RB = D * 2;                 // bytes per cache row
+  constexpr int PPR = D / 8;                // 16-byte pieces per row
+  constexpr int TILE = MMA_ROWS * RB;       // bytes of a K (or V) chunk
+  constexpr int NT = D / 8;                 // n-tiles of O
+  extern __shared__ uint4 mma_ring[];       // [WARPS][MMA_ST][K tile | V tile]
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;    // fragment coordinates: query row g, column pair t
+  uint8_t* ring = reinterpret_cast<uint8_t*>(mma_ring) + warp * (MMA_ST * 2 * TILE);
+
+  long long q_pos0 = p.q_pos0;
+  int S = p.S, rows_per_split = p.rows_per_split;
+  if (p.pos_ptr) {
+    q_pos0 = *p.pos_ptr;
+    long long n = q_pos0 + 1 - p.k_pos0;
+    if (p.stripe_n > 0) {
+      n = striped_rows(q_pos0, p.stripe_n, p.stripe_rank, p.stripe_base, p.stripe_len0);
+      q_pos0 = -1;
+    }
+    S = static_cast<int>(n < 0 ? 0 : (n > p.S ? p.S : n));
+    rows_per_split = (S + p.splits - 1) / p.splits;
+    if (rows_per_split < 1) rows_per_split = 1;
+  }
+  const int r0 = split * rows_per_split;
+  const int r1 = min(S, r0 + rows_per_split);
+  const __nv_bfloat16* kb = p.k + b * p.k_sb + h * p.k_sh;
+  const __nv_bfloat16* vb = p.v + b * p.v_sb + h * p.v_sh;
+
+  // Q fragments: a0 = Q[g][16ks + 2t, +1], a2 = Q[g][16ks + 8 + 2t, +1]; rows >= QL are zero
+  uint32_t qa[D / 16][2];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    qa[ks][0] = qa[ks][1] = 0u;
+    if (g < QL) {
+      const __nv_bfloat16* qr = p.q + ((static_cast<long long>(b) * QL + g) * p.H + h) * D + 16 * ks + 2 * t;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qr);
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(qr + 8);
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m = -INFINITY, l = 0.f;  // of query row g; l is this lane's share of the row sum
+
+  // chunk c of this warp starts at row r0 + (warp + WARPS * c) * 16
+  auto issue = [&](int c, int slot) {
+    const int base = r0 + (warp + WARPS * c) * MMA_ROWS;
+    uint8_t* kt = ring + slot * 2 * TILE;
+#pragma unroll
+    for (int j = 0; j < MMA_ROWS * PPR / 32; ++j) {
+      const int piece = lane + 32 * j;
+      const int row = piece / PPR, ch = piece % PPR;
+      const int r = base + row;
+      const bool in = r < r1;
+      const long long rr = in ? r : r0;  // a valid address; not read when !in (the piece is zero-filled)
+      const int off = row * RB + ((ch ^ (row & 7)) << 4);
+      cp_async16(kt + off, kb + rr * p.k_ss + ch * 8, in ? 16 : 0);
+      cp_async16(kt + TILE + off, vb + rr * p.v_ss + ch * 8, in ? 16 : 0);
+    }
+  };
+  const int my_rows = r1 - (r0 + warp * MMA_ROWS);
+  const int n_chunks = my_rows <= 0 ? 0 : (my_rows + WARPS * MMA_ROWS - 1) / (WARPS * MMA_ROWS);
+#pragma unroll
+  for (int i = 0; i < MMA_ST - 1; ++i) {
+    if (i < n_chunks) issue(i, i);
+    cp_async_commit();  // one group per chunk, empty or not: the group count in the wait below is a constant
+  }
+  int slot = 0;
+  for (int c = 0; c < n_chunks; ++c) {
+    __syncwarp();  // every lane is done with the stage that is filled next
+    if (c + MMA_ST - 1 < n_chunks) issue(c + MMA_ST - 1, (slot + MMA_ST - 1) % MMA_ST);
+    cp_async_commit();
+    cp_async_wait<MMA_ST - 1>();
+    __syncwarp();  // the other lanes' pieces of chunk c are in too
+    const uint8_t* kt = ring + slot * 2 * TILE;
+    const uint8_t* vt = kt + TILE;
+    const int base = r0 + (warp + WARPS * c) * MMA_ROWS;
+
+    // ---- S = Q K^T: s[nt] holds row g, cache rows base + 8 nt + 2t, +1
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+    {
+      const int mat = lane >> 3, rr = lane & 7;
+      const int row = rr + 8 * (mat >> 1);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int ch = 2 * ks + (mat & 1);
+        uint32_t bf[4];
+        ldmatrix_x4(bf, kt + row * RB + ((ch ^ (row & 7)) << 4));
+        mma_16816_top(s[0], qa[ks][0], qa[ks][1], bf[0], bf[1]);
+        mma_16816_top(s[1], qa[ks][0], qa[ks][1], bf[2], bf[3]);
+      }
+    }
+    // ---- mask, online softmax of row g over the 16 cache rows
+    float x[2][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int r = base + 8 * nt + 2 * t + e;
+        bool vis = r < r1 && g < QL;
+        if (q_pos0 >= 0) vis = vis && (p.k_pos0 + r <= q_pos0 + g);
+        if (p.mask && vis) vis = p.mask[b * p.m_sb + h * p.m_sh + g * p.m_sq + r] != 0;
+        x[nt][e] = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, x[nt][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m - m_use);  // 0 when m is -inf
+    float pr[2][2];
+    float psum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[nt][e] = exp2f(x[nt][e] - m_use);
+        psum += pr[nt][e];
+      }
+    l = l * alpha + psum;
+    m = m_new;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      o[j][0] *= alpha;
+      o[j][1] *= alpha;
+    }
+    // ---- O += P V: P as the A fragment (a0: cache rows 2t, 2t+1; a2: rows 8 + 2t, +1)
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(pr[0][0], pr[0][1]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(pr[1][0], pr[1][1]);
+    const uint32_t a0 = *reinterpret_cast<uint32_t*>(&p0), a2 = *reinterpret_cast<uint32_t*>(&p1);
+    {
+      const int mat = lane >> 3, rr = lane & 7;
+      const int row = rr + 8 * (mat & 1);
+#pragma unroll
+      for (int j = 0; j < NT / 2; ++j) {
+        const int ch = 2 * j + (mat >> 1);
+        uint32_t bf[4];
+        ldmatrix_x4_trans(bf, vt + row * RB + ((ch ^ (row & 7)) << 4));
+        mma_16816_top(o[2 * j], a0, a2, bf[0], bf[1]);
+        mma_16816_top(o[2 * j + 1], a0, a2, bf[2], bf[3]);
+      }
+    }
+    slot = slot + 1 == MMA_ST ? 0 : slot + 1;
+  }
+  cp_async_wait<0>();  // only empty groups can be left
+
+  // ---- the row sum over the four lanes of a row, then the warps of the CTA (as in the kernel above)
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  __shared__ float sm_m[WARPS][8], sm_l[WARPS][8];
+  __shared__ float sm_o[WARPS][8][D];
+  if (t == 0) {
+    sm_m[warp][g] = m;
+    sm_l[warp][g] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    sm_o[warp][g][8 * j + 2 * t] = o[j][0];
+    sm_o[warp][g][8 * j + 2 * t + 1] = o[j][1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < QL * D; idx += THREADS) {
+    const int i = idx / D, d = idx % D;
+    float mxw = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mxw = fmaxf(mxw, sm_m[w][i]);
+    const float mu = mxw == -INFINITY ? 0.f : mxw;
+    float lt = 0.f, ot = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float a = exp2f(sm_m[w][i] - mu);
+      lt += sm_l[w][i] * a;
+      ot += sm_o[w][i][d] * a;
+    }
+    const long long pi = ((static_cast<long long>(b) * p.H + h) * QL + i) * p.splits + split;
+    p.o_part[pi * D + d] = lt > 0.f ? ot / lt : 0.f;
+    if (d == 0) p.lse_part[pi] = lt > 0.f ? (mxw + log2f(lt)) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
 struct MergeParams {
   const float* o_part;    // element (row, part, d) at row*o_rs + part*o_ps + d
   const float* lse_part;  // element (row, part) at row*l_rs + part*l_ps
@@ -756,6 +980,7 @@ struct RaDecodeArgs {
   long long stripe_base, stripe_len0;
   void* stream;
   int stages;  // 0, 3 or 4: depth of the asynchronous-copy ring of the cache rows (0: loads into registers)
+  int mma;     // 1: the tensor-core kernel (any q_len <= 8), 0: the CUDA-core kernel
 };
 
 extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
@@ -791,6 +1016,22 @@ extern "C" int ra_decode_splitkv(const RaDecodeArgs* a) {
   if (ql != a->QL) {
     set_error("ra_decode_splitkv: q_len must be 1, 2, 4 or 8 (pad the query)");
     return kHostBadArg;
+  }
+  if (a->mma) {
+    constexpr int kRing128 = WARPS * MMA_ST * 2 * MMA_ROWS * 128 * 2, kRing64 = WARPS * MMA_ST * 2 * MMA_ROWS * 64 * 2;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_done[dev]) {  // with the static arrays the 128-wide variant needs more than 48 KB
+      cudaFuncSetAttribute(decode_splitkv_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing128);
+      cudaFuncSetAttribute(decode_splitkv_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing64);
+      attr_done[dev] = true;
+    }
+    if (a->D == 128)
+      decode_splitkv_mma_kernel<128><<<grid, THREADS, kRing128, s>>>(p, a->QL);
+    else
+      decode_splitkv_mma_kernel<64><<<grid, THREADS, kRing64, s>>>(p, a->QL);
+    return check_launch("decode_splitkv_mma_kernel");
   }
   if (a->stages != 0 && a->stages != 3 && a->stages != 4) {
     set_error("ra_decode_splitkv: stages must be 0, 3 or 4");

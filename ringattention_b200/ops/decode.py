@@ -24,6 +24,11 @@ c_vp = ctypes.c_void_p
 STAGES = int(os.environ.get("RINGATTN_B200_DECODE_STAGES", "3"))
 
 
+# Calls with at least this many query rows per cache row go to the tensor-core form of the split-KV kernel (the
+# CUDA-core form spends q times the instructions per cache row).
+MMA_MIN_ROWS = int(os.environ.get("RINGATTN_B200_DECODE_MMA_MIN_ROWS", "2"))
+
+
 class _DecodeArgs(ctypes.Structure):
     _fields_ = [
         ("q", c_vp), ("k", c_vp), ("v", c_vp),
@@ -39,6 +44,7 @@ class _DecodeArgs(ctypes.Structure):
         ("stripe_base", c_ll), ("stripe_len0", c_ll),
         ("stream", c_vp),
         ("stages", ctypes.c_int),
+        ("mma", ctypes.c_int),
     ]
 
 
@@ -92,6 +98,7 @@ def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, 
     a.stripe_n, a.stripe_rank, a.stripe_base, a.stripe_len0 = stripe if stripe is not None else (0, 0, 0, 0)
     a.stream = torch.cuda.current_stream().cuda_stream
     a.stages = STAGES
+    a.mma = int(QL >= MMA_MIN_ROWS)
     _lib.call("ra_decode_splitkv", ctypes.byref(a))
     return o_part, lse_part
 

@@ -131,6 +131,10 @@ def main(argv=None) -> int:
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--decode-stages", type=int, default=None, choices=[0, 3, 4],
                     help="decode: depth of the asynchronous-copy ring of the cache rows (default: the library's)")
+    ap.add_argument("--q-rows", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="decode: query rows per cache row (streams sharing the cache)")
+    ap.add_argument("--decode-mma-min-rows", type=int, default=None,
+                    help="decode: use the tensor-core kernel from this many query rows (default: the library's)")
     ap.add_argument("--prologue", default="none", choices=["none", "rmsnorm", "swiglu"],
                     help="small_m_linear: apply RMSNorm or SwiGLU to the input inside the kernel")
     ap.add_argument("--cache-layout", default="heads", choices=["rows", "heads"],
@@ -205,7 +209,7 @@ def main(argv=None) -> int:
         from ..ops import decode as Dk
 
         B, S, H, D = args.batch, args.seq, args.heads, args.head_dim
-        q = torch.randn(B, 1, H, D, device=dev).bfloat16()
+        q = torch.randn(B, args.q_rows, H, D, device=dev).bfloat16()
         if args.cache_layout == "rows":
             cache = torch.randn(B, S, 2, H, D, device=dev).bfloat16()
             ck, cv = cache[:, :, 0], cache[:, :, 1]
@@ -214,8 +218,12 @@ def main(argv=None) -> int:
             ck, cv = cache[:, 0].permute(0, 2, 1, 3), cache[:, 1].permute(0, 2, 1, 3)
         if args.decode_stages is not None:
             Dk.STAGES = args.decode_stages
+        if args.decode_mma_min_rows is not None:
+            Dk.MMA_MIN_ROWS = args.decode_mma_min_rows
         fn = lambda: Dk.decode_partial(q, ck, cv, q_pos0=S, k_pos0=0)
         res["cache_layout"] = args.cache_layout
+        res["q_rows"] = args.q_rows
+        res["tensor_core_kernel"] = args.q_rows >= Dk.MMA_MIN_ROWS
         res["stages"] = Dk.STAGES
         flops = 4.0 * B * S * H * D
         bytes_ = 2.0 * B * S * H * D * 2
