@@ -909,6 +909,129 @@ __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bflo
   }
 }
 
+// The same product on the tensor cores, for 2..8 rows (several decode streams): with M rows the kernels above spend
+// M times the FMAs per weight and become bound by their instruction stream (M = 4: 94 us against 34 us for M = 1 on
+// 22016 x 4096). Here the rows of f(x) are the M side of a 16 x 8 x 16 MMA (rows >= M are zero) and eight output columns
+// its N side. The order of the contraction is free, so a lane keeps the 16 bytes it loads together: lane (g, t) of a
+// warp reads W[col0 + g][kb + 8t .. 8t + 7] (eight rows x 64 contiguous bytes per load instruction) and uses the four
+// register halves as {b0, b1} of two consecutive k-steps; the A fragments are the same eight elements of f(x)[g] from
+// shared memory. One LDG.128, one LDS.128 and two MMAs per 16 bytes of weights, no unpacking and no cross-lane
+// reduction: the accumulator of lane (g, t) IS y[g][col0 + 2t .. 2t + 1] once the k loop ends. The eight warps of a
+// CTA split K (32-element blocks dealt round-robin, so the CTA reads 512 contiguous bytes of a row at a time) and add
+// their accumulators through shared memory. f(x) is built once per CTA; the grid is sized to be resident at once
+// and every CTA walks several column tiles.
+constexpr int LM_THREADS = 256, LM_WARPS = 8, LM_UNROLL = 8;
+
+// 16-byte read-only load that the compiler may not move: the LM_UNROLL loads of a round all leave before the first
+// MMA that consumes one of them.
+__device__ __forceinline__ uint4 ldg_stream_v4(const uint4* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
+template <int PRO>  // 0: f(x) = x, PRO_RMSNORM, PRO_SWIGLU
+__global__ void __launch_bounds__(LM_THREADS) small_m_linear_mma_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                        const __nv_bfloat16* __restrict__ w,
+                                                                        __nv_bfloat16* __restrict__ y,
+                                                                        const __nv_bfloat16* __restrict__ res,
+                                                                        const __nv_bfloat16* __restrict__ gain,
+                                                                        float eps, int M, int N, int K) {
+  extern __shared__ uint4 lm_smem[];
+  const int n16 = K / 8;
+  const int ldx16 = n16 + 4;  // row stride of xs in 16-byte units: 64 bytes of padding keep LDS.128 conflict-free
+  uint4* xs = lm_smem;        // [M][ldx16]
+  __shared__ float red[LM_WARPS][8][8];  // [warp][row][column of the tile]
+  __shared__ float ssq[LM_WARPS][8];
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- prologue: f(x) -> shared memory (RMSNorm without its rstd factor, which multiplies the sums at the end)
+  for (int m = 0; m < M; ++m) {
+    float ss = 0.f;
+    const long long ldx = PRO == PRO_SWIGLU ? 2ll * K : K;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + m * ldx);
+    for (int c = tid; c < n16; c += LM_THREADS) {
+      if (PRO == 0) {
+        xs[m * ldx16 + c] = xr[c];
+        continue;
+      }
+      float xf[8], of[8];
+      unpack8(xr[c], xf);
+      unpack8(PRO == PRO_SWIGLU ? xr[c + n16] : reinterpret_cast<const uint4*>(gain)[c], of);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (PRO == PRO_RMSNORM) {
+          ss = fmaf(xf[e], xf[e], ss);
+          xf[e] *= of[e];
+        } else {
+          xf[e] = xf[e] / (1.f + __expf(-xf[e])) * of[e];  // same arithmetic as the stand-alone activation kernel
+        }
+      }
+      xs[m * ldx16 + c] = pack8(xf);
+    }
+    if (PRO == PRO_RMSNORM) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) ssq[wid][m] = ss;
+    }
+  }
+  __syncthreads();
+
+  const int n_tiles = (N + 7) / 8;
+  const int n_kb = (K + 31) / 32;                       // 32-element blocks of K; warp `wid` takes wid, wid + 8, ...
+  const int my_kb = wid < n_kb ? (n_kb - wid + LM_WARPS - 1) / LM_WARPS : 0;
+  const uint4* xrow = xs + (g < M ? g : 0) * ldx16;     // rows >= M multiply zeros
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int col0 = tile * 8;
+    const int col = min(col0 + g, N - 1);               // past the end: a valid row, its sums are not stored
+    const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(col) * K);
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i0 = 0; i0 < my_kb; i0 += LM_UNROLL) {
+      uint4 wv[LM_UNROLL];
+      int pc[LM_UNROLL];
+#pragma unroll
+      for (int u = 0; u < LM_UNROLL; ++u) {
+        pc[u] = (wid + LM_WARPS * (i0 + u)) * 4 + t;    // 16-byte piece of the row
+        const bool in = i0 + u < my_kb && pc[u] < n16;
+        wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (in) wv[u] = ldg_stream_v4(wr + pc[u]);
+        if (!in) pc[u] = 0;
+      }
+#pragma unroll
+      for (int u = 0; u < LM_UNROLL; ++u) {
+        uint4 xv = xrow[pc[u]];
+        if (g >= M) xv = make_uint4(0u, 0u, 0u, 0u);
+        mma_16816_top(d, xv.x, xv.y, wv[u].x, wv[u].y);
+        mma_16816_top(d, xv.z, xv.w, wv[u].z, wv[u].w);
+      }
+    }
+    red[wid][g][2 * t] = d[0];
+    red[wid][g][2 * t + 1] = d[1];
+    __syncthreads();
+    if (tid < M * 8) {
+      const int m = tid >> 3, c = tid & 7;
+      float v = 0.f;
+#pragma unroll
+      for (int k = 0; k < LM_WARPS; ++k) v += red[k][m][c];
+      if (PRO == PRO_RMSNORM) {
+        float tsum = 0.f;
+#pragma unroll
+        for (int k = 0; k < LM_WARPS; ++k) tsum += ssq[k][m];
+        v *= rsqrtf(tsum / K + eps);
+      }
+      if (col0 + c < N) {
+        const long long o = static_cast<long long>(m) * N + col0 + c;
+        if (res) v += __bfloat162float(res[o]);
+        if (RA_IN_BOUNDS(col0 + c, 1, N, kTagSmallMLinear)) y[o] = __float2bfloat16(v);
+      }
+    }
+    __syncthreads();  // red is rewritten by the next tile
+  }
+}
+
 // One decode token per sequence: rotate the q and k heads of the (B, 1, 3, H, D) qkv buffer in place (RoPE at the
 // position in *pos_ptr) and append the rotated K and the V to the cache shard when this rank owns the position
 // (same ownership rule and cache views as kv_append_kernel). One launch instead of two per layer and token.
@@ -1220,6 +1343,62 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
   }
 #undef RA_SML_CASE
   return check_launch("small_m_linear_pro_kernel");
+}
+
+namespace {
+template <int PRO>
+int launch_linear_mma(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, const __nv_bfloat16* res,
+                      const __nv_bfloat16* gain, float eps, int M, int N, int K, cudaStream_t s) {
+  using namespace ra::decode;
+  const int smem = M * (K * 2 + 64);
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = dev < 64 ? dev : 63;
+  auto kern = small_m_linear_mma_kernel<PRO>;
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      set_error("ra_small_m_linear_mma: cannot raise the shared-memory limit");
+      return kHostLaunchFail;
+    }
+    attr_done[dev] = true;
+  }
+  // the whole grid resident at once: 8 CTAs of 256 threads per SM unless shared memory allows fewer
+  int per_sm = (220 * 1024) / (smem + 3 * 1024);
+  per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+  const int n_tiles = (N + 7) / 8;
+  int blocks = sm_count() * per_sm;
+  if (blocks > n_tiles) blocks = n_tiles;
+  // the same number of tiles for every CTA where that costs less than a quarter of the grid
+  const int rounds = (n_tiles + blocks - 1) / blocks;
+  const int even = (n_tiles + rounds - 1) / rounds;
+  if (even * 4 >= blocks * 3) blocks = even;
+  kern<<<blocks, LM_THREADS, smem, s>>>(x, w, y, res, gain, eps, M, N, K);
+  return check_launch("small_m_linear_mma_kernel");
+}
+}  // namespace
+
+// y = f(x) W^T (+ res) for 1 <= M <= 8 rows on the tensor cores; prologue 0 (none), 1 (RMSNorm, needs gain), 2
+// (SwiGLU: x is (M, 2K)). M * (K * 2 + 64) bytes of shared memory, at most 200 KB.
+extern "C" int ra_small_m_linear_mma(const void* x, const void* w, void* y, const void* res, const void* gain,
+                                     float eps, int prologue, int M, int N, int K, void* stream) {
+  using namespace ra::decode;
+  if (M < 1 || M > 8 || K % 8 || N < 1 || prologue < 0 || prologue > PRO_SWIGLU ||
+      (prologue == PRO_RMSNORM && !gain) || static_cast<long long>(M) * (K * 2 + 64) > 200 * 1024) {
+    set_error("ra_small_m_linear_mma: need 1 <= M <= 8, K % 8 == 0, M * (2 K + 64) <= 200 KB, a prologue of 0 (none), "
+              "1 (RMSNorm, with a gain) or 2 (SwiGLU)");
+    return kHostBadArg;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
+  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
+  const __nv_bfloat16* gg = static_cast<const __nv_bfloat16*>(gain);
+  if (prologue == 0) return launch_linear_mma<0>(xx, ww, yy, rr, gg, eps, M, N, K, s);
+  if (prologue == PRO_RMSNORM) return launch_linear_mma<PRO_RMSNORM>(xx, ww, yy, rr, gg, eps, M, N, K, s);
+  return launch_linear_mma<PRO_SWIGLU>(xx, ww, yy, rr, gg, eps, M, N, K, s);
 }
 
 extern "C" int ra_rope_append(void* qkv, void* k_cache, void* v_cache, long long sb, long long ss, long long sh,

@@ -135,6 +135,8 @@ def main(argv=None) -> int:
                     help="decode: query rows per cache row (streams sharing the cache)")
     ap.add_argument("--decode-mma-min-rows", type=int, default=None,
                     help="decode: use the tensor-core kernel from this many query rows (default: the library's)")
+    ap.add_argument("--linear-mma-min-rows", type=int, default=None,
+                    help="small_m_linear: use the tensor-core kernel from this many rows (default: the library's)")
     ap.add_argument("--prologue", default="none", choices=["none", "rmsnorm", "swiglu"],
                     help="small_m_linear: apply RMSNorm or SwiGLU to the input inside the kernel")
     ap.add_argument("--cache-layout", default="heads", choices=["rows", "heads"],
@@ -247,6 +249,9 @@ def main(argv=None) -> int:
             else:
                 K.small_m_linear(x, ws[turn[0]])
 
+        if args.linear_mma_min_rows is not None:
+            K.LINEAR_MMA_MIN_ROWS = args.linear_mma_min_rows
+        res["tensor_core_kernel"] = K._mma_linear_ok(M, Kd)
         res["prologue"] = args.prologue
 
         flops = 2.0 * M * N * Kd
