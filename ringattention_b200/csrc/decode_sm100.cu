@@ -910,125 +910,113 @@ __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bflo
 }
 
 // The same product on the tensor cores, for 2..8 rows (several decode streams): with M rows the kernels above spend
-// M times the FMAs per weight and become bound by their instruction stream (M = 4: 94 us against 34 us for M = 1 on
-// 22016 x 4096). Here the rows of f(x) are the M side of a 16 x 8 x 16 MMA (rows >= M are zero) and eight output columns
-// its N side. The order of the contraction is free, so a lane keeps the 16 bytes it loads together: lane (g, t) of a
-// warp reads W[col0 + g][kb + 8t .. 8t + 7] (eight rows x 64 contiguous bytes per load instruction) and uses the four
-// register halves as {b0, b1} of two consecutive k-steps; the A fragments are the same eight elements of f(x)[g] from
-// shared memory. One LDG.128, one LDS.128 and two MMAs per 16 bytes of weights, no unpacking and no cross-lane
-// reduction: the accumulator of lane (g, t) IS y[g][col0 + 2t .. 2t + 1] once the k loop ends. The eight warps of a
-// CTA split K (32-element blocks dealt round-robin, so the CTA reads 512 contiguous bytes of a row at a time) and add
-// their accumulators through shared memory. f(x) is built once per CTA; the grid is sized to be resident at once
-// and every CTA walks several column tiles.
-constexpr int LM_THREADS = 256, LM_WARPS = 8, LM_UNROLL = 8;
+// M times the FMAs per weight and become bound by their instruction stream (M = 8: 189 us against 34 us for M = 1 on
+// 22016 x 4096). Built like decode_splitkv_mma_kernel: the rows of x are the M side of a 16 x 8 x 16 MMA (rows >= M are
+// zero), 16 weight rows (output columns) a chunk's N side, and K is walked in chunks of 128. A warp owns 16 output
+// columns and a quarter of K; it stages its chunks (16 weight rows x 256 bytes, and the matching 128 elements of the
+// eight x rows) through its own three-stage cp.async ring, XOR-swizzled for ldmatrix, with __syncwarp() as the only
+// synchronisation in the loop; the four warps of a CTA add their accumulators through shared memory at the end.
+// (Loading the B fragments straight from global memory, eight rows x 64 bytes per instruction, reached only 2.5
+// TB/s; staged like this the weight stream is read in 256-byte row segments.) x is taken as it is: RMSNorm or
+// SwiGLU run as their own launches before it on this path.
+constexpr int LM_THREADS = 128, LM_WARPS = 4, LM_ST = 3, LM_KC = 128, LM_COLS = 16;
+constexpr int LM_WTILE = LM_COLS * LM_KC * 2;     // bytes of a weight chunk
+constexpr int LM_XTILE = 8 * LM_KC * 2;           // bytes of an x chunk (eight rows)
+constexpr int LM_STAGE = LM_WTILE + LM_XTILE;
 
-// 16-byte read-only load that the compiler may not move: the LM_UNROLL loads of a round all leave before the first
-// MMA that consumes one of them.
-__device__ __forceinline__ uint4 ldg_stream_v4(const uint4* ptr) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(ptr));
-  return v;
-}
-
-template <int PRO>  // 0: f(x) = x, PRO_RMSNORM, PRO_SWIGLU
 __global__ void __launch_bounds__(LM_THREADS) small_m_linear_mma_kernel(const __nv_bfloat16* __restrict__ x,
                                                                         const __nv_bfloat16* __restrict__ w,
                                                                         __nv_bfloat16* __restrict__ y,
-                                                                        const __nv_bfloat16* __restrict__ res,
-                                                                        const __nv_bfloat16* __restrict__ gain,
-                                                                        float eps, int M, int N, int K) {
-  extern __shared__ uint4 lm_smem[];
-  const int n16 = K / 8;
-  const int ldx16 = n16 + 4;  // row stride of xs in 16-byte units: 64 bytes of padding keep LDS.128 conflict-free
-  uint4* xs = lm_smem;        // [M][ldx16]
-  __shared__ float red[LM_WARPS][8][8];  // [warp][row][column of the tile]
-  __shared__ float ssq[LM_WARPS][8];
-  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+                                                                        const __nv_bfloat16* __restrict__ res, int M,
+                                                                        int N, int K) {
+  extern __shared__ uint4 lm_ring[];  // [LM_WARPS][LM_ST][weights | x]
+  __shared__ float red[LM_WARPS][8][LM_COLS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  uint8_t* ring = reinterpret_cast<uint8_t*>(lm_ring) + warp * (LM_ST * LM_STAGE);
+  const int col0 = blockIdx.x * LM_COLS;
+  const int n_kc = (K + LM_KC - 1) / LM_KC;  // chunks of K; warp w takes chunks w, w + 4, ... (the CTA reads 1 KB of a row at a time)
+  const int my_kc = warp < n_kc ? (n_kc - warp + LM_WARPS - 1) / LM_WARPS : 0;
 
-  // ---- prologue: f(x) -> shared memory (RMSNorm without its rstd factor, which multiplies the sums at the end)
-  for (int m = 0; m < M; ++m) {
-    float ss = 0.f;
-    const long long ldx = PRO == PRO_SWIGLU ? 2ll * K : K;
-    const uint4* xr = reinterpret_cast<const uint4*>(x + m * ldx);
-    for (int c = tid; c < n16; c += LM_THREADS) {
-      if (PRO == 0) {
-        xs[m * ldx16 + c] = xr[c];
-        continue;
-      }
-      float xf[8], of[8];
-      unpack8(xr[c], xf);
-      unpack8(PRO == PRO_SWIGLU ? xr[c + n16] : reinterpret_cast<const uint4*>(gain)[c], of);
+  auto issue = [&](int c, int slot) {
+    const int k0 = (warp + LM_WARPS * c) * LM_KC;
+    uint8_t* wt = ring + slot * LM_STAGE;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (PRO == PRO_RMSNORM) {
-          ss = fmaf(xf[e], xf[e], ss);
-          xf[e] *= of[e];
-        } else {
-          xf[e] = xf[e] / (1.f + __expf(-xf[e])) * of[e];  // same arithmetic as the stand-alone activation kernel
-        }
-      }
-      xs[m * ldx16 + c] = pack8(xf);
+    for (int j = 0; j < LM_COLS * 16 / 32; ++j) {   // 16 rows x 16 pieces of 16 bytes
+      const int piece = lane + 32 * j;
+      const int row = piece >> 4, ch = piece & 15;
+      const int col = col0 + row;
+      const bool in = col < N && k0 + ch * 8 < K;
+      const __nv_bfloat16* src = w + static_cast<long long>(in ? col : 0) * K + (in ? k0 + ch * 8 : 0);
+      cp_async16(wt + row * (LM_KC * 2) + ((ch ^ (row & 7)) << 4), src, in ? 16 : 0);
     }
-    if (PRO == PRO_RMSNORM) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) ssq[wid][m] = ss;
+    for (int j = 0; j < 8 * 16 / 32; ++j) {         // 8 rows x 16 pieces
+      const int piece = lane + 32 * j;
+      const int row = piece >> 4, ch = piece & 15;
+      const bool in = row < M && k0 + ch * 8 < K;
+      const __nv_bfloat16* src = x + static_cast<long long>(in ? row : 0) * K + (in ? k0 + ch * 8 : 0);
+      cp_async16(wt + LM_WTILE + row * (LM_KC * 2) + ((ch ^ (row & 7)) << 4), src, in ? 16 : 0);
     }
+  };
+#pragma unroll
+  for (int i = 0; i < LM_ST - 1; ++i) {
+    if (i < my_kc) issue(i, i);
+    cp_async_commit();  // one group per chunk, empty or not
+  }
+  float acc[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+  int slot = 0;
+  const int mat = lane >> 3, rr = lane & 7;
+  for (int c = 0; c < my_kc; ++c) {
+    __syncwarp();  // every lane is done with the stage that is filled next
+    if (c + LM_ST - 1 < my_kc) issue(c + LM_ST - 1, (slot + LM_ST - 1) % LM_ST);
+    cp_async_commit();
+    cp_async_wait<LM_ST - 1>();
+    __syncwarp();
+    const uint8_t* wt = ring + slot * LM_STAGE;
+    const uint8_t* xt = wt + LM_WTILE;
+#pragma unroll
+    for (int ks2 = 0; ks2 < LM_KC / 32; ++ks2) {  // two k-steps of 16 per round
+      // A fragments of both k-steps with one ldmatrix: matrices (x rows 0-7, 16-byte piece 4 ks2 + mat)
+      uint32_t af[4];
+      {
+        const int ch = 4 * ks2 + mat;
+        ldmatrix_x4(af, xt + rr * (LM_KC * 2) + ((ch ^ (rr & 7)) << 4));
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // B fragments: (weight rows 0-7 | 8-15) x (piece 2 ks | 2 ks + 1) with ks = 2 ks2 + h
+        const int row = rr + 8 * (mat >> 1);
+        const int ch = 2 * (2 * ks2 + h) + (mat & 1);
+        uint32_t bf[4];
+        ldmatrix_x4(bf, wt + row * (LM_KC * 2) + ((ch ^ (row & 7)) << 4));
+        mma_16816_top(acc[0], af[2 * h], af[2 * h + 1], bf[0], bf[1]);
+        mma_16816_top(acc[1], af[2 * h], af[2 * h + 1], bf[2], bf[3]);
+      }
+    }
+    slot = slot + 1 == LM_ST ? 0 : slot + 1;
+  }
+  cp_async_wait<0>();
+  // ---- the four warps' sums of y[row g][col0 + 8 nt + 2t, +1]
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    red[warp][g][8 * nt + 2 * t] = acc[nt][0];
+    red[warp][g][8 * nt + 2 * t + 1] = acc[nt][1];
   }
   __syncthreads();
-
-  const int n_tiles = (N + 7) / 8;
-  const int n_kb = (K + 31) / 32;                       // 32-element blocks of K; warp `wid` takes wid, wid + 8, ...
-  const int my_kb = wid < n_kb ? (n_kb - wid + LM_WARPS - 1) / LM_WARPS : 0;
-  const uint4* xrow = xs + (g < M ? g : 0) * ldx16;     // rows >= M multiply zeros
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int col0 = tile * 8;
-    const int col = min(col0 + g, N - 1);               // past the end: a valid row, its sums are not stored
-    const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(col) * K);
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int i0 = 0; i0 < my_kb; i0 += LM_UNROLL) {
-      uint4 wv[LM_UNROLL];
-      int pc[LM_UNROLL];
+  for (int i = threadIdx.x; i < M * LM_COLS; i += LM_THREADS) {
+    const int m = i / LM_COLS, c = i % LM_COLS;
+    if (col0 + c >= N) continue;
+    float v = 0.f;
 #pragma unroll
-      for (int u = 0; u < LM_UNROLL; ++u) {
-        pc[u] = (wid + LM_WARPS * (i0 + u)) * 4 + t;    // 16-byte piece of the row
-        const bool in = i0 + u < my_kb && pc[u] < n16;
-        wv[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (in) wv[u] = ldg_stream_v4(wr + pc[u]);
-        if (!in) pc[u] = 0;
-      }
-#pragma unroll
-      for (int u = 0; u < LM_UNROLL; ++u) {
-        uint4 xv = xrow[pc[u]];
-        if (g >= M) xv = make_uint4(0u, 0u, 0u, 0u);
-        mma_16816_top(d, xv.x, xv.y, wv[u].x, wv[u].y);
-        mma_16816_top(d, xv.z, xv.w, wv[u].z, wv[u].w);
-      }
-    }
-    red[wid][g][2 * t] = d[0];
-    red[wid][g][2 * t + 1] = d[1];
-    __syncthreads();
-    if (tid < M * 8) {
-      const int m = tid >> 3, c = tid & 7;
-      float v = 0.f;
-#pragma unroll
-      for (int k = 0; k < LM_WARPS; ++k) v += red[k][m][c];
-      if (PRO == PRO_RMSNORM) {
-        float tsum = 0.f;
-#pragma unroll
-        for (int k = 0; k < LM_WARPS; ++k) tsum += ssq[k][m];
-        v *= rsqrtf(tsum / K + eps);
-      }
-      if (col0 + c < N) {
-        const long long o = static_cast<long long>(m) * N + col0 + c;
-        if (res) v += __bfloat162float(res[o]);
-        if (RA_IN_BOUNDS(col0 + c, 1, N, kTagSmallMLinear)) y[o] = __float2bfloat16(v);
-      }
-    }
-    __syncthreads();  // red is rewritten by the next tile
+    for (int k = 0; k < LM_WARPS; ++k) v += red[k][m][c];
+    const long long o = static_cast<long long>(m) * N + col0 + c;
+    if (res) v += __bfloat162float(res[o]);
+    if (RA_IN_BOUNDS(col0 + c, 1, N, kTagSmallMLinear)) y[o] = __float2bfloat16(v);
   }
 }
 
@@ -1345,60 +1333,32 @@ extern "C" int ra_small_m_linear_fused(const void* x, const void* w, void* y, co
   return check_launch("small_m_linear_pro_kernel");
 }
 
-namespace {
-template <int PRO>
-int launch_linear_mma(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, const __nv_bfloat16* res,
-                      const __nv_bfloat16* gain, float eps, int M, int N, int K, cudaStream_t s) {
+// y = x W^T (+ res) for 1 <= M <= 8 rows on the tensor cores (x as it is: no prologue on this path).
+extern "C" int ra_small_m_linear_mma(const void* x, const void* w, void* y, const void* res, int M, int N, int K,
+                                     void* stream) {
   using namespace ra::decode;
-  const int smem = M * (K * 2 + 64);
+  if (M < 1 || M > 8 || K % 8 || N < 1) {
+    set_error("ra_small_m_linear_mma: need 1 <= M <= 8 and K % 8 == 0");
+    return kHostBadArg;
+  }
+  constexpr int smem = LM_WARPS * LM_ST * LM_STAGE;  // 72 KB
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  dev = dev < 64 ? dev : 63;
-  auto kern = small_m_linear_mma_kernel<PRO>;
-  if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(small_m_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess) {
       cudaGetLastError();
       set_error("ra_small_m_linear_mma: cannot raise the shared-memory limit");
       return kHostLaunchFail;
     }
     attr_done[dev] = true;
   }
-  // the whole grid resident at once: 8 CTAs of 256 threads per SM unless shared memory allows fewer
-  int per_sm = (220 * 1024) / (smem + 3 * 1024);
-  per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
-  const int n_tiles = (N + 7) / 8;
-  int blocks = sm_count() * per_sm;
-  if (blocks > n_tiles) blocks = n_tiles;
-  // the same number of tiles for every CTA where that costs less than a quarter of the grid
-  const int rounds = (n_tiles + blocks - 1) / blocks;
-  const int even = (n_tiles + rounds - 1) / rounds;
-  if (even * 4 >= blocks * 3) blocks = even;
-  kern<<<blocks, LM_THREADS, smem, s>>>(x, w, y, res, gain, eps, M, N, K);
+  const int blocks = (N + LM_COLS - 1) / LM_COLS;
+  small_m_linear_mma_kernel<<<blocks, LM_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<const __nv_bfloat16*>(res), M, N, K);
   return check_launch("small_m_linear_mma_kernel");
-}
-}  // namespace
-
-// y = f(x) W^T (+ res) for 1 <= M <= 8 rows on the tensor cores; prologue 0 (none), 1 (RMSNorm, needs gain), 2
-// (SwiGLU: x is (M, 2K)). M * (K * 2 + 64) bytes of shared memory, at most 200 KB.
-extern "C" int ra_small_m_linear_mma(const void* x, const void* w, void* y, const void* res, const void* gain,
-                                     float eps, int prologue, int M, int N, int K, void* stream) {
-  using namespace ra::decode;
-  if (M < 1 || M > 8 || K % 8 || N < 1 || prologue < 0 || prologue > PRO_SWIGLU ||
-      (prologue == PRO_RMSNORM && !gain) || static_cast<long long>(M) * (K * 2 + 64) > 200 * 1024) {
-    set_error("ra_small_m_linear_mma: need 1 <= M <= 8, K % 8 == 0, M * (2 K + 64) <= 200 KB, a prologue of 0 (none), "
-              "1 (RMSNorm, with a gain) or 2 (SwiGLU)");
-    return kHostBadArg;
-  }
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
-  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
-  __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
-  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
-  const __nv_bfloat16* gg = static_cast<const __nv_bfloat16*>(gain);
-  if (prologue == 0) return launch_linear_mma<0>(xx, ww, yy, rr, gg, eps, M, N, K, s);
-  if (prologue == PRO_RMSNORM) return launch_linear_mma<PRO_RMSNORM>(xx, ww, yy, rr, gg, eps, M, N, K, s);
-  return launch_linear_mma<PRO_SWIGLU>(xx, ww, yy, rr, gg, eps, M, N, K, s);
 }
 
 extern "C" int ra_rope_append(void* qkv, void* k_cache, void* v_cache, long long sb, long long ss, long long sh,

@@ -213,22 +213,21 @@ def cast_bf16_to_f32(src, dst):
 
 # From this many rows the small-M products run on the tensor cores (mma.sync with the rows of x as the M side): the
 # CUDA-core kernels spend M times the FMAs per weight and fall behind the weight stream.
-LINEAR_MMA_MIN_ROWS = int(os.environ.get("RINGATTN_B200_LINEAR_MMA_MIN_ROWS", "9"))
+LINEAR_MMA_MIN_ROWS = int(os.environ.get("RINGATTN_B200_LINEAR_MMA_MIN_ROWS", "2"))
 
 
-def _mma_linear_ok(M: int, Kd: int) -> bool:
-    return LINEAR_MMA_MIN_ROWS <= M <= 8 and M * (2 * Kd + 64) <= 200 * 1024
+def _mma_linear_ok(M: int) -> bool:
+    return LINEAR_MMA_MIN_ROWS <= M <= 8
 
 
-def _small_m_linear_mma(x, w, residual, gain, eps, prologue, out=None):
+def _small_m_linear_mma(x, w, residual, out=None):
     M = x.shape[0]
     N, Kd = w.shape
     if out is None:
         out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
     assert out.is_contiguous() and out.shape == (M, N) and x.is_contiguous() and w.is_contiguous()
-    assert residual is None or residual.is_contiguous()
-    _lib.call("ra_small_m_linear_mma", ptr(x), ptr(w), ptr(out), ptr(residual), ptr(gain), c_f(eps), prologue,
-              M, N, Kd, stream_ptr())
+    assert x.shape[1] == Kd and (residual is None or residual.is_contiguous())
+    _lib.call("ra_small_m_linear_mma", ptr(x), ptr(w), ptr(out), ptr(residual), M, N, Kd, stream_ptr())
     return out
 
 
@@ -241,8 +240,8 @@ def small_m_linear(x, w, out=None, residual=None):
     if out is None:
         out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
     assert out.is_contiguous() and (residual is None or residual.is_contiguous())
-    if _mma_linear_ok(M, Kd):
-        return _small_m_linear_mma(x, w, residual, None, 0.0, 0, out=out)
+    if _mma_linear_ok(M):
+        return _small_m_linear_mma(x, w, residual, out=out)
     _lib.call("ra_small_m_linear", ptr(x), ptr(w), ptr(out), ptr(residual), M, N, Kd, stream_ptr())
     return out
 
@@ -277,8 +276,9 @@ def norm_linear(x, gain, eps: float, w, out=None):
     """``rmsnorm(x) W^T``. For a handful of rows (decode) the normalisation runs in the prologue of the
     weight-streaming kernel: one launch; otherwise the RMSNorm kernel and the GEMM."""
     assert x.shape[1] == w.shape[1]
-    if x.is_contiguous() and x.dtype == torch.bfloat16 and _mma_linear_ok(x.shape[0], w.shape[1]):
-        return _small_m_linear_mma(x, w, None, gain, eps, 1, out=out)
+    if x.is_contiguous() and x.dtype == torch.bfloat16 and _mma_linear_ok(x.shape[0]):
+        h, _ = rmsnorm_fwd(x, gain, eps)  # several rows: the tensor-core kernel takes x as it is
+        return _small_m_linear_mma(h, w, None, out=out)
     if _fused_small_m_ok(x, w):
         return _small_m_linear_fused(x, w, None, gain, eps, 1, out=out)
     h, _ = rmsnorm_fwd(x, gain, eps)
@@ -289,9 +289,9 @@ def swiglu_linear(gu, w, residual=None, out=None):
     """``(silu(gate) * up) W^T (+ residual)`` from the fused gate/up projection ``gu (M, 2F)``; one launch for
     a handful of rows."""
     assert gu.shape[1] == 2 * w.shape[1]
-    if gu.is_contiguous() and gu.dtype == torch.bfloat16 and _mma_linear_ok(gu.shape[0], w.shape[1]) and \
+    if gu.is_contiguous() and gu.dtype == torch.bfloat16 and _mma_linear_ok(gu.shape[0]) and \
             (residual is None or residual.is_contiguous()):
-        return _small_m_linear_mma(gu, w, residual, None, 0.0, 2, out=out)
+        return _small_m_linear_mma(swiglu_fwd(gu), w, residual, out=out)
     if _fused_small_m_ok(gu, w, residual):
         return _small_m_linear_fused(gu, w, residual, None, 0.0, 2, out=out)
     return linear_auto(swiglu_fwd(gu), w, out=out, residual=residual)

@@ -251,7 +251,7 @@ def main(argv=None) -> int:
 
         if args.linear_mma_min_rows is not None:
             K.LINEAR_MMA_MIN_ROWS = args.linear_mma_min_rows
-        res["tensor_core_kernel"] = K._mma_linear_ok(M, Kd)
+        res["tensor_core_kernel"] = K._mma_linear_ok(M)
         res["prologue"] = args.prologue
 
         flops = 2.0 * M * N * Kd
