@@ -919,7 +919,10 @@ __global__ void __launch_bounds__(256) small_m_linear_pro_kernel(const __nv_bflo
 // (Loading the B fragments straight from global memory, eight rows x 64 bytes per instruction, reached only 2.5
 // TB/s; staged like this the weight stream is read in 256-byte row segments.) x is taken as it is: RMSNorm or
 // SwiGLU run as their own launches before it on this path.
-constexpr int LM_THREADS = 128, LM_WARPS = 4, LM_ST = 3, LM_KC = 128, LM_COLS = 16;
+#ifndef RA_LM_ST
+#define RA_LM_ST 3  // ring depth; measured 2 / 3 / 4 on 4 x 4096 x 11008: 26.9 / 19.5 / 19.4 us, on 4 x 22016 x 4096: 34.2 / 33.8 / 35.7 us
+#endif
+constexpr int LM_THREADS = 128, LM_WARPS = 4, LM_ST = RA_LM_ST, LM_KC = 128, LM_COLS = 16;
 constexpr int LM_WTILE = LM_COLS * LM_KC * 2;     // bytes of a weight chunk
 constexpr int LM_XTILE = 8 * LM_KC * 2;           // bytes of an x chunk (eight rows)
 constexpr int LM_STAGE = LM_WTILE + LM_XTILE;
