@@ -3,14 +3,19 @@
 // The reference's inference op rotates the whole KV cache around the ring for every call
 // (ringattention/ringattention_inference.py:17-33). Here each GPU reads its own shard exactly once:
 //   1. decode_splitkv_kernel : the shard is cut into `splits` row ranges, one CTA per (range, head,
-//      batch). A few query rows (QL <= 8) are held in registers; K/V stream from HBM with 16-byte
-//      loads, several rows in flight per thread; online softmax in fp32; each CTA emits a partial
-//      (o, lse) for its range.
-//   2. decode_merge_kernel   : merges partials with log-sum-exp weights. In the ring variant the
-//      merged per-GPU result is *stored into every peer's inbox* (plain stores to peer memory), and
-//      after a flag barrier the same kernel merges the N per-GPU partials; every rank ends up with
-//      the identical result, as the reference's rotation would give.
-// The work is a batched GEMV: HBM bandwidth is the roofline, so it runs on the CUDA cores.
+//      batch). A few query rows (QL <= 8) are held in registers; K/V stream from HBM as 16-byte pieces
+//      through a per-thread cp.async ring; online softmax in fp32; each CTA emits a partial (o, lse)
+//      for its range. One query row: a batched GEMV on the CUDA cores at the speed of a plain copy.
+//      decode_splitkv_mma_kernel is the same pass for 2-8 query rows (streams sharing a cache) with the
+//      query rows as the M side of mma.sync m16n8k16, per-warp cp.async ring and ldmatrix.
+//   2. decode_merge_kernel   : merges partials with log-sum-exp weights. decode_merge_exchange_kernel
+//      does that for a ring in one launch: the merged per-GPU result is *stored into every peer's
+//      inbox* (plain stores to peer memory), a per-row flag is released on every rank, and after a
+//      bounded wait for the same row of every rank the N per-GPU partials are merged; every rank ends
+//      up with the identical result, as the reference's rotation would give.
+// The file also holds the other kernels of a decode step: the weight-streaming linears for a handful of
+// rows (CUDA cores with RMSNorm / SwiGLU prologues for one row, mma.sync for 2-8 rows), RoPE + cache
+// append, and the device-side step counters that make the step replayable as one CUDA graph.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
