@@ -141,6 +141,34 @@ def test_merge_exchange_gives_up_on_a_silent_peer_and_still_merges_its_own_rows(
     assert Dk.exchange_fits(rows) and not Dk.exchange_fits(10 ** 6)
 
 
+def test_cuda_core_kernels_still_serve_several_rows(monkeypatch):
+    """Calls with 2-8 rows go to the tensor-core kernels by default; with the thresholds raised the CUDA-core
+    kernels (which serve one row by default) take them and give the same answers."""
+    from ringattention_b200.ops import decode as Dk, kernels as K, reference as R
+    from ringattention_b200.parallel.mesh import resolve_axis
+
+    torch.manual_seed(5)
+    B, QL, H, D, S = 1, 4, 2, 128, 900
+    q = torch.randn(B, QL, H, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    v = torch.randn_like(k)
+    x = torch.randn(4, 1024, device="cuda").bfloat16()
+    g = (1 + 0.1 * torch.randn(1024, device="cuda")).bfloat16()
+    w = (torch.randn(520, 1024, device="cuda") / 32).bfloat16()
+    outs = []
+    for rows in (2, 9):
+        monkeypatch.setattr(Dk, "MMA_MIN_ROWS", rows)
+        monkeypatch.setattr(K, "LINEAR_MMA_MIN_ROWS", rows)
+        o = Dk.ring_decode_attention(q, k, v, None, resolve_axis(None), n_valid=S, q_pos0=S - QL, k_pos0=0)
+        outs.append((o.float(), K.norm_linear(x, g, 1e-5, w).float(), K.small_m_linear(x, w).float()))
+    ref = R.dense_attention(q, k, v, torch.arange(S - QL, S, device="cuda"), torch.arange(S, device="cuda"),
+                            causal_block_size=1, dtype=torch.float32)
+    for o, _, _ in outs:
+        assert (o - ref).abs().max() < 0.02
+    assert (outs[0][1] - outs[1][1]).abs().max() <= 0.02 * outs[1][1].abs().max() + 0.02
+    assert (outs[0][2] - outs[1][2]).abs().max() <= 0.01 * outs[1][2].abs().max() + 0.02
+
+
 def test_prefill_and_greedy_decode_match_full_forward():
     from ringattention_b200.config import LlamaConfig
     from ringattention_b200.models.llama_infer import LlamaInference
