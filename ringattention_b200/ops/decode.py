@@ -60,12 +60,16 @@ def _pad_q(q: torch.Tensor):
     return q.contiguous(), ql, tgt
 
 
-def default_splits(S: int, B: int, H: int) -> int:
+def default_splits(S: int, B: int, H: int, mma: bool = False) -> int:
     """Many small CTAs: measured on a 128K-row, 32-head shard, 18 splits (4 CTAs per SM in total) gave
-    4.57 TB/s, 74 splits 4.65 (a ragged last wave), 256 splits 5.19. At least 512 cache rows per CTA."""
+    4.57 TB/s, 74 splits 4.65 (a ragged last wave), 256 splits 5.19 with register loads; with the asynchronous-copy
+    ring 64 to 512 splits are within 3 % of each other (6.83 to 7.02 TB/s). At least 512 cache rows per CTA.
+    The tensor-core kernel (``mma``) has two CTAs of four warps per SM and likes half as many, longer ranges: four
+    query rows, 128 / 256 / 512 splits: 0.315 / 0.332 / 0.408 ms."""
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    want = max(1, (64 * sms) // max(1, B * H))
-    return max(1, min(want, (S + 511) // 512, 512))
+    per_sm, rows = (32, 1024) if mma else (64, 512)
+    want = max(1, (per_sm * sms) // max(1, B * H))
+    return max(1, min(want, (S + rows - 1) // rows, 512))
 
 
 def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, k_pos0: int = 0,
@@ -75,7 +79,7 @@ def decode_partial(q, k, v, *, n_valid: Optional[int] = None, q_pos0: int = -1, 
     ``(o_part (B*H*QL, splits, D), lse_part (B*H*QL, splits), QL_padded)``."""
     B, QL, H, D = q.shape
     S = k.shape[1] if n_valid is None else int(n_valid)
-    splits = splits or default_splits(S, B, H)
+    splits = splits or default_splits(S, B, H, mma=QL >= MMA_MIN_ROWS)
     rows = B * H * QL
     o_part = torch.empty(rows, splits, D, device=q.device, dtype=torch.float32)
     lse_part = torch.empty(rows, splits, device=q.device, dtype=torch.float32)

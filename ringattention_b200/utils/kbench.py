@@ -131,6 +131,7 @@ def main(argv=None) -> int:
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--decode-stages", type=int, default=None, choices=[0, 3, 4],
                     help="decode: depth of the asynchronous-copy ring of the cache rows (default: the library's)")
+    ap.add_argument("--splits", type=int, default=0, help="decode: row ranges per (batch, head); 0 = the library's choice")
     ap.add_argument("--q-rows", type=int, default=1, choices=[1, 2, 4, 8],
                     help="decode: query rows per cache row (streams sharing the cache)")
     ap.add_argument("--decode-mma-min-rows", type=int, default=None,
@@ -222,14 +223,14 @@ def main(argv=None) -> int:
             Dk.STAGES = args.decode_stages
         if args.decode_mma_min_rows is not None:
             Dk.MMA_MIN_ROWS = args.decode_mma_min_rows
-        fn = lambda: Dk.decode_partial(q, ck, cv, q_pos0=S, k_pos0=0)
+        fn = lambda: Dk.decode_partial(q, ck, cv, q_pos0=S, k_pos0=0, splits=args.splits or None)
         res["cache_layout"] = args.cache_layout
         res["q_rows"] = args.q_rows
         res["tensor_core_kernel"] = args.q_rows >= Dk.MMA_MIN_ROWS
         res["stages"] = Dk.STAGES
         flops = 4.0 * B * S * H * D
         bytes_ = 2.0 * B * S * H * D * 2
-        res.update(shape=[B, S, H, D], splits=Dk.default_splits(S, B, H))
+        res.update(shape=[B, S, H, D], splits=args.splits or Dk.default_splits(S, B, H, mma=args.q_rows >= Dk.MMA_MIN_ROWS))
     elif args.kernel == "small_m_linear":
         # y[M, N] = x[M, K] W[N, K]^T with M <= 8 (decode-time projections): weight bandwidth is the roofline
         M, N, Kd = min(args.m, 8), args.n, args.k
